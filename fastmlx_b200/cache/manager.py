@@ -119,6 +119,8 @@ class CacheManager:
         total = 0
         for g in self.groups:
             n = req.length if g.spec.window <= 0 else min(req.length, g.spec.window + g.spec.keep_first)
+            if g.spec.chunk > 0:
+                n = req.length % g.spec.chunk + 1
             total += g.spec.num_kv_heads * g.spec.token_width * e * len(g.entries) * n
         return total
 
@@ -145,6 +147,8 @@ class CacheManager:
             w = g.spec.window
             kept = -(-g.spec.keep_first // self.page_size) * self.page_size
             need = n_tokens if w <= 0 else min(n_tokens, w + min(portion, n_tokens) + self.page_size + kept)
+            if g.spec.chunk > 0:        # the running run of positions, and a portion that may reach over its end
+                need = min(n_tokens, g.spec.chunk + min(portion, n_tokens) + self.page_size)
             if need > room:
                 return room
         return 0
@@ -221,11 +225,12 @@ class CacheManager:
         req.reserved, req._new_pages = 0, []
         for gi, (g, bt) in enumerate(zip(self.groups, req.tables)):
             w = g.spec.window
-            if w <= 0:
+            if w <= 0 and g.spec.chunk <= 0:
                 continue
             # the next query sits at position >= length and sees keys > position - w; the pages of the
-            # first tokens that every query keeps seeing stay
-            first_needed = req.length - w + 1
+            # first tokens that every query keeps seeing stay.  With runs of c positions it sees no key in front
+            # of its own run, which starts at or behind the run that position `length` lies in
+            first_needed = req.length - w + 1 if w > 0 else req.length - req.length % g.spec.chunk
             bt.kept = max(bt.kept, min(-(-g.spec.keep_first // self.page_size), len(bt.pages)))
             bt.first_live = max(bt.first_live, bt.kept)
             while bt.first_live < len(bt.pages) and (bt.first_live + 1) * self.page_size <= first_needed:

@@ -82,8 +82,9 @@ class Engine:
         per_group = []
         for g in probe.groups:
             n = max(1, pages)
-            if g.spec.window > 0:
-                n = min(n, ec.max_concurrent_requests * (-(-(g.spec.window + portion) // ec.block_size) + 1))
+            held = g.spec.window if g.spec.window > 0 else g.spec.chunk       # a window, or runs of positions
+            if held > 0:
+                n = min(n, ec.max_concurrent_requests * (-(-(held + portion) // ec.block_size) + 1))
             per_group.append(n)
         self.manager = CacheManager(needs, page_size=ec.block_size, num_pages=per_group or max(1, pages),
                                     max_requests=ec.max_concurrent_requests, dtype=self.rt.dtype,

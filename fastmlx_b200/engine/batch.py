@@ -24,6 +24,7 @@ class GroupMeta:
     block_tables: torch.Tensor         # int32 [R, max_blocks]; -1 = page given back / not there
     slot_mapping: torch.Tensor         # int64 [T]: page * page_size + offset of each token
     window: int = 0
+    chunk: int = 0                     # keys are seen within runs of this many positions (0: no such mask)
 
 
 @dataclass
@@ -222,7 +223,8 @@ def build_context(entries, manager, device, status, *, pad_rows: int = 0, pad_bl
     groups = []
     for g in range(ngroups):
         groups.append(GroupMeta(ps, dview(f"bt{g}").view(Rp, max_blocks),
-                                dview(f"sm{g}").view(torch.int64), manager.groups[g].spec.window))
+                                dview(f"sm{g}").view(torch.int64), manager.groups[g].spec.window,
+                                getattr(manager.groups[g].spec, "chunk", 0)))
     return StepContext(
         T=Tp, R=Rp, tokens=dview("tokens"), positions=dview("positions"), token_row=dview("token_row"),
         row_start=dview("row_start"), row_ctx=dview("row_ctx"), row_slot=dview("row_slot"),

@@ -2,3 +2,4 @@
 from . import llama  # noqa: F401
 from . import gekavik  # noqa: F401
 from . import medirax  # noqa: F401
+from . import sorupel  # noqa: F401

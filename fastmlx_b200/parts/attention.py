@@ -33,6 +33,14 @@ class GQAAttention(Mixer):
     heads' outputs are multiplied element by element with sigmoid(W_g x), W_g of the output's width, before the
     output projection; it rides in the q/k/v product.  `late_bias`: the q/k/v product leaves in 32-bit and the
     biases are added, in 32-bit, by the kernel that normalises and rotates (a gate has no bias).
+
+    And these.  `values_from_keys`: there is no value projection; a token's values are its keys as projected, before
+    norm and rotation (values as wide as keys).  `qk_norm_whole` (with `qk_norm_first` and weights): q and k are
+    divided by the root mean square of the whole projection, all heads at once, and the weights have the
+    projection's width.  `chunk` c > 0 (instead of a window): position i sees j <= i only where i // c == j // c,
+    runs counted from position 0 of the request whatever the cut of its prompt; the cache gives earlier runs' pages
+    back.  `sink` s: the softmax's denominator has one more term exp(s) that has no value (s = 0 adds one).
+    `gate_per_head`: the gate has one value per head, not one per output element.
     """
 
     supports_cuda_graph = True
@@ -44,7 +52,8 @@ class GQAAttention(Mixer):
                  softcap: float = 0.0, qk_norm_eps: float | None = None, output: bool = True,
                  weight_suffix: str = ".weight", bias_suffix: str = ".bias", qk_norm_weights=None,
                  qk_norm_first: bool = False, keep_first: int = 0, gate: str | None = None, late_bias: bool = False,
-                 out_bias: bool | None = None):
+                 out_bias: bool | None = None, values_from_keys: bool = False, qk_norm_whole: bool = False,
+                 chunk: int = 0, sink: float | None = None, gate_per_head: bool = False):
         if num_heads % num_kv_heads:
             raise ValueError(f"{num_heads} query heads are no multiple of {num_kv_heads} kv heads")
         self.nh, self.nkv, self.hd = int(num_heads), int(num_kv_heads), int(head_dim)
@@ -55,12 +64,22 @@ class GQAAttention(Mixer):
         self.qk_norm_first, self.keep_first = bool(qk_norm_first), int(keep_first)
         self.gate_name = f"{name}.{gate}" if gate else None
         self.late_bias = bool(late_bias) and bool(bias)
+        self.values_from_keys, self.qk_norm_whole = bool(values_from_keys), bool(qk_norm_whole)
+        self.chunk, self.sink, self.gate_per_head = int(chunk or 0), None if sink is None else float(sink), bool(gate_per_head)
+        if self.chunk and window:
+            raise ValueError("a layer masks by a window or by runs of positions, not both")
+        if self.values_from_keys and (self.vd != self.hd or share_kv):
+            raise ValueError("values that are the keys have the keys' width and a cache of their own")
+        if self.qk_norm_whole and not (self.qk_norm_weights and qk_norm_first):
+            raise ValueError("the norm over the whole projection comes before the rotation and has weights")
+        self.sinks = None
         if self.keep_first and not window:
             self.keep_first = 0                         # without a window every token is seen anyway
         if (self.qk_norm_weights or self.qk_norm_first) and self.qk_norm_eps is None:
             raise ValueError("a weight or an order for the q/k norm needs its eps")
         self.general = (self.softcap > 0 or self.qk_norm_eps is not None or self.vd != self.hd or self.keep_first > 0
-                        or self.gate_name is not None or self.late_bias)
+                        or self.gate_name is not None or self.late_bias or self.values_from_keys or self.chunk > 0
+                        or self.sink is not None)
         self.scale = float(scale) if scale is not None else float(head_dim) ** -0.5
         self.window = int(window)
         self.share_kv = bool(share_kv)
@@ -68,12 +87,12 @@ class GQAAttention(Mixer):
         qn, kn, vn, on = (f"{name}.{p}" for p in proj_names)
         outs = [(qn, self.nh * self.hd)]
         if not share_kv:
-            outs += [(kn, self.nkv * self.hd), (vn, self.nkv * self.vd)]
+            outs += [(kn, self.nkv * self.hd)] + ([] if self.values_from_keys else [(vn, self.nkv * self.vd)])
         self.qkv_features = sum(o for _, o in outs)
         self.bias_names = [(n + bias_suffix, o) for n, o in outs] if self.late_bias else []
         self.inner_features = self.nh * self.vd
         if self.gate_name:
-            outs = outs + [(self.gate_name, self.inner_features)]
+            outs = outs + [(self.gate_name, self.nh if self.gate_per_head else self.inner_features)]
         self.qkv = Linear(width, outs, bias and not self.late_bias, weight_suffix=weight_suffix, bias_suffix=bias_suffix)
         out_bias = bool(bias) if out_bias is None else bool(out_bias)
         self.out_piece = (on + weight_suffix, self.inner_features, on + bias_suffix if out_bias else None)
@@ -87,7 +106,8 @@ class GQAAttention(Mixer):
     def own_weight_specs(self):
         specs = [WeightSpec(n, (o,), "bias") for n, o in self.bias_names]
         if self.qk_norm_weights:
-            specs += [WeightSpec(n, (self.hd,), "norm") for n in self.qk_norm_weights]
+            widths = (self.nh * self.hd, self.nkv * self.hd) if self.qk_norm_whole else (self.hd, self.hd)
+            specs += [WeightSpec(n, (w,), "norm") for n, w in zip(self.qk_norm_weights, widths)]
         return specs
 
     def bind_own(self, tensors, rt: Runtime):
@@ -95,12 +115,15 @@ class GQAAttention(Mixer):
             self.row_bias = torch.cat([to_f32_vector(tensors[n], rt) for n, _ in self.bias_names]).contiguous()
         if self.qk_norm_weights:
             self.q_weight, self.k_weight = (to_f32_vector(tensors[n], rt) for n in self.qk_norm_weights)
+        if self.sink is not None:
+            self.sinks = torch.full((self.nh,), self.sink, dtype=torch.float32, device=rt.device)
 
     def weight_bytes(self):
         return super().weight_bytes() + 4 * (len(self.bias_names) and self.qkv_features)
 
     def cache_spec(self):
-        return PagedKVSpec(self.nkv, self.hd, self.window, 0 if self.vd == self.hd else self.vd, self.keep_first)
+        return PagedKVSpec(self.nkv, self.hd, self.window, 0 if self.vd == self.hd else self.vd, self.keep_first,
+                           False, self.chunk)
 
     def forward(self, x, ctx, cache):
         return self.o.forward(self.forward_inner(x, ctx, cache))
@@ -120,12 +143,23 @@ class GQAAttention(Mixer):
         inv_freq, rot, trad = self.pos.native_args()
         g = ctx.groups[cache.group]
         store = cache.writable and not self.share_kv
+        more = dict(whole=True, values_from_keys=self.values_from_keys) if self.qk_norm_whole or self.values_from_keys else {}
         q = k.qk_prepare(qkv, ctx.positions, inv_freq, rot, trad, self.qk_norm_eps, g.slot_mapping if store else None,
                          cache.kv if store else None, self.nh, self.nkv, self.hd, self.vd, ctx.status,
                          **(dict(bias=self.row_bias, q_weight=self.q_weight, k_weight=self.k_weight,
                                  norm_first=self.qk_norm_first) if extended or self.q_weight is not None or self.qk_norm_first
-                            else {}))
+                            else {}), **more)
         gate = qkv[:, self.qkv_features:] if self.gate_name else None
+        if self.chunk or self.sinks is not None or self.gate_per_head:
+            # runs of positions, a term without a value in the denominator, one gate value per head
+            opts = dict(chunk=self.chunk, sinks=self.sinks, gate=gate, gate_group=self.vd if self.gate_per_head else 1)
+            wide_ex = getattr(k, "wide_attention_takes", None)
+            if wide_ex is not None and wide_ex(q, cache.kv, self.hd, self.vd, out):
+                return k.paged_attention_wide(q, cache.kv, ctx, g, self.nh, self.nkv, self.hd, self.scale, self.softcap,
+                                              self.window, out=out, keep_first=self.keep_first, **opts)
+            return k.paged_attention_general(q, cache.kv, ctx, g, self.nh, self.nkv, self.hd, self.vd, self.scale,
+                                             self.softcap, self.window, g.page_size, out=out, keep_first=self.keep_first,
+                                             **opts)
         if extended or self.keep_first:
             wide_ex = getattr(k, "wide_attention_takes", None)
             if wide_ex is not None and wide_ex(q, cache.kv, self.hd, self.vd, out):

@@ -37,13 +37,16 @@ class PagedKVSpec:
     `keep_first` > 0 beside a window: the request's first keep_first tokens stay visible to
     every later query, so the pages that hold them are never given back.  `values_are_keys`:
     a page holds keys only and attention reads them as values too (a cached latent from which
-    both are read out)."""
+    both are read out).  `chunk` = c > 0 (instead of a window): a query sees the keys of its own
+    run of c positions only, runs counted from position 0, so the pages of earlier runs are
+    given back."""
     num_kv_heads: int
     head_dim: int
     window: int = 0
     v_head_dim: int = 0
     keep_first: int = 0
     values_are_keys: bool = False
+    chunk: int = 0
 
     @property
     def value_dim(self) -> int:

@@ -3,7 +3,7 @@ from __future__ import annotations
 
 import torch
 
-from .base import Part, Runtime, WeightSpec, to_compute
+from .base import Part, Runtime, StateSpec, WeightSpec, to_compute
 
 
 class Embedding(Part):
@@ -23,7 +23,12 @@ class Embedding(Part):
     def weight_bytes(self):
         return 0          # a step reads T rows, not the table
 
-    def forward(self, ids, ctx):
+    def state_spec(self):
+        """Per-request state of the embedding itself (none here); a part that has some gets a state slot from the
+        cache manager and is called with it, `forward(ids, ctx, cache)`."""
+        return None
+
+    def forward(self, ids, ctx, cache=None):
         if self.weight.dtype != self.rt.dtype:          # a table stored in 32-bit under bfloat16 activations
             return self.rt.k.embedding(ids, self.weight, ctx.status, self.rt.dtype)
         return self.rt.k.embedding(ids, self.weight, ctx.status)
@@ -34,6 +39,40 @@ class Embedding(Part):
         out = b.reg(self.width)
         b.op(OP_EMBED, out0=out, w=b.ptr(self.weight), w_dtype=_dt(self.weight.dtype), n=self.width, table_rows=self.vocab)
         return out
+
+
+class BigramEmbedding(Embedding):
+    """h[t] = E[id_t] + B[(id_(t-1) * mul_prev + id_t * mul_cur) mod buckets]: a second table addressed by a hash
+    of the token and the one before it; a sequence's first token takes the table's last row (row `buckets`).
+
+    The token before a step's first one is part of the request's state: one integer per request slot, read by
+    the first token of each row of the step and replaced by the row's last token.  The two rows are summed in
+    32-bit and the sum is the stream's first value, so beside bfloat16 activations the part hands on a 32-bit
+    stream (`starts_stream`)."""
+
+    starts_stream = True
+    supports_cuda_graph = True
+
+    def __init__(self, vocab: int, width: int, name: str, bigram: str, buckets: int, mul_prev: int, mul_cur: int,
+                 suffix: str = ".weight"):
+        super().__init__(vocab, width, name, suffix)
+        self.buckets, self.mul_prev, self.mul_cur = int(buckets), int(mul_prev), int(mul_cur)
+        self.bigram_tensor = bigram + suffix
+        self.bigram = None
+
+    def own_weight_specs(self):
+        return super().own_weight_specs() + [WeightSpec(self.bigram_tensor, (self.buckets + 1, self.width), "embedding")]
+
+    def bind_own(self, tensors, rt: Runtime):
+        super().bind_own(tensors, rt)
+        self.bigram = to_compute(tensors[self.bigram_tensor], rt)
+
+    def state_spec(self):
+        return StateSpec((1,), torch.int32)
+
+    def forward(self, ids, ctx, cache=None):
+        return self.rt.k.embed_bigram(ids, self.weight, self.bigram, ctx, cache.state, self.buckets, self.mul_prev,
+                                      self.mul_cur)
 
 
 class LMHead(Part):

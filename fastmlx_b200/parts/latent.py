@@ -25,55 +25,122 @@ class LatentAttention(Mixer):
     sight out of the latents once per step, into pages of their own that live for the step, and attend over those
     with the heads' own sizes.  The cache holds latents either way.
 
-    Tensors, under `name`: dq, dq.norm, uq, dkv, dkv.norm, uk, uv, g (optional), o."""
+    Tensors, under `name`: dq, dq.norm, uq, dkv, dkv.norm, uk, uv, g (optional), o.
+
+    A second form, chosen by its parameters.  `q_rank` = 0: the queries are one projection `q` of the input, no latent
+    of their own.  `rot_dim` R > 0: a query head is [dim unrotated | R rotated] values; the down-projection `dkv` has R
+    more rows, which are not normalised, are rotated by the token's position (pairs (i, i + R/2), angles
+    position * rot_base^(-2i/R), 32-bit) and are one key part shared by all heads, so that a score is
+    (q_unrotated . W_uk,h c + q_rotated . k_rotated) * scale.  The cache row of a token is then [c | rotated part], and
+    a query is carried to [W_uk,h^T q_unrotated | q_rotated]; the values are read out of the row's first kv_rank
+    entries.  `sink`: a tensor of one learned number per head whose exponential is one more term of the softmax's
+    denominator (it has no key and no value and is not scaled).  `gate` = "element": the gate has one value per
+    output element (`True`: one per head).  `share_kv`: the layer has no `dkv` and reads the rows that the schedule
+    entry it is pointed at has cached."""
 
     supports_cuda_graph = True
     LONG_PORTION = 128
 
     def __init__(self, width: int, num_heads: int, head_dim: int, v_head_dim: int, q_rank: int, kv_rank: int,
-                 eps: float, name: str, scale: float | None = None, window: int = 0, gate: bool = True,
-                 weight_suffix: str = "", norm_suffix: str = ".norm"):
+                 eps: float, name: str, scale: float | None = None, window: int = 0, gate: bool | str = True,
+                 weight_suffix: str = "", norm_suffix: str = ".norm", rot_dim: int = 0, rot_base: float = 10000.0,
+                 sink: str | None = None, share_kv: bool = False):
         self.width, self.nh, self.hd, self.vd = int(width), int(num_heads), int(head_dim), int(v_head_dim)
         self.q_rank, self.kv_rank, self.eps = int(q_rank), int(kv_rank), float(eps)
         self.scale = float(scale) if scale is not None else float(head_dim) ** -0.5
         self.window = int(window)
         self.name, self.wsfx = name, weight_suffix
-        downs = [(f"{name}.dq", self.q_rank), (f"{name}.dkv", self.kv_rank)]
-        if gate:
-            downs.append((f"{name}.g", self.nh))
+        self.rot, self.rot_base, self.share_kv = int(rot_dim), float(rot_base), bool(share_kv)
+        if self.rot % 2:
+            raise ValueError(f"the rotated part has an even width, not {self.rot}")
+        self.row = self.kv_rank + self.rot                 # what a token's cache row holds
+        self.direct = self.q_rank == 0                     # queries straight from the input
+        if (self.rot or self.share_kv or sink) and not self.direct:
+            raise ValueError("a rotated part, a term in the denominator and a shared cache go with direct queries")
+        self.gate_group = 0 if not gate else (1 if gate == "element" else self.vd)
         self.has_gate = bool(gate)
-        self.down = Linear(width, downs, False, weight_suffix=weight_suffix)         # one product reads x
-        self.uq = Linear(self.q_rank, [(f"{name}.uq", self.nh * self.hd)], False, weight_suffix=weight_suffix)
+        self.sink_name = f"{name}.{sink}" if sink else None
+        self.sinks = self.inv_freq = None
+        downs = [] if self.direct else [(f"{name}.dq", self.q_rank)]
+        if not self.share_kv:
+            downs.append((f"{name}.dkv", self.row))
+        if gate:
+            downs.append((f"{name}.g", self.nh * self.vd // self.gate_group))
+        self.down = Linear(width, downs, False, weight_suffix=weight_suffix) if downs else None     # one product reads x
+        if self.direct:
+            self.uq = Linear(width, [(f"{name}.q", self.nh * (self.hd + self.rot))], False, weight_suffix=weight_suffix)
+        else:
+            self.uq = Linear(self.q_rank, [(f"{name}.uq", self.nh * self.hd)], False, weight_suffix=weight_suffix)
         self.o = Linear(self.nh * self.vd, [(f"{name}.o", width)], False, weight_suffix=weight_suffix)
         self.norm_names = (f"{name}.dq{norm_suffix}", f"{name}.dkv{norm_suffix}")
         self.uk_name, self.uv_name = f"{name}.uk{weight_suffix}", f"{name}.uv{weight_suffix}"
 
     def children(self):
-        return (self.down, self.uq, self.o)
+        return tuple(p for p in (self.down, self.uq, self.o) if p is not None)
 
     def own_weight_specs(self):
-        return [WeightSpec(self.norm_names[0], (self.q_rank,), "norm"), WeightSpec(self.norm_names[1], (self.kv_rank,), "norm"),
-                WeightSpec(self.uk_name, (self.nh * self.hd, self.kv_rank), "matrix"),
-                WeightSpec(self.uv_name, (self.nh * self.vd, self.kv_rank), "matrix")]
+        specs = [] if self.direct else [WeightSpec(self.norm_names[0], (self.q_rank,), "norm")]
+        if not self.share_kv:
+            specs.append(WeightSpec(self.norm_names[1], (self.kv_rank,), "norm"))
+        if self.sink_name:
+            specs.append(WeightSpec(self.sink_name, (self.nh,), "bias"))
+        return specs + [WeightSpec(self.uk_name, (self.nh * self.hd, self.kv_rank), "matrix"),
+                        WeightSpec(self.uv_name, (self.nh * self.vd, self.kv_rank), "matrix")]
 
     def bind_own(self, tensors, rt: Runtime):
-        self.q_norm, self.c_norm = (to_f32_vector(tensors[n], rt) for n in self.norm_names)
+        self.q_norm = None if self.direct else to_f32_vector(tensors[self.norm_names[0]], rt)
+        self.c_norm = None if self.share_kv else to_f32_vector(tensors[self.norm_names[1]], rt)
+        if self.sink_name:
+            self.sinks = to_f32_vector(tensors[self.sink_name], rt)
+        if self.rot:
+            from .rope import inverse_frequencies
+            self.inv_freq = inverse_frequencies(self.rot, self.rot_base).to(torch.float32).to(rt.device).contiguous()
         uk = to_compute(tensors[self.uk_name], rt).view(self.nh, self.hd, self.kv_rank)
         # carrying a query into the latent's space multiplies by W_uk,h^T: [H, kv_rank, dim]
         self.uk_t = uk.transpose(1, 2).contiguous()
         self.uv = to_compute(tensors[self.uv_name], rt).view(self.nh, self.vd, self.kv_rank).contiguous()
         # long portions: every head's keys, then every head's values, in one product over the latents in sight
         self.ukv = None
-        if rt.dtype == torch.bfloat16 and self.hd == self.vd and self.hd % 16 == 0 and self.hd <= 256 and rt.device.type == "cuda":
+        if not self.direct and rt.dtype == torch.bfloat16 and self.hd == self.vd and self.hd % 16 == 0 and self.hd <= 256 and rt.device.type == "cuda":
             self.ukv = torch.cat([uk.reshape(self.nh * self.hd, self.kv_rank), self.uv.view(self.nh * self.vd, self.kv_rank)], 0).contiguous()
 
     def weight_bytes(self):
         return super().weight_bytes() + (self.uk_t.numel() + self.uv.numel()) * self.uk_t.element_size()
 
     def cache_spec(self):
-        return PagedKVSpec(1, self.kv_rank, self.window, 0, 0, True)
+        return PagedKVSpec(1, self.row, self.window, 0, 0, True)
+
+    def forward_direct(self, x, ctx, cache):
+        """The form with direct queries (and, where rot_dim > 0, a rotated part beside the latent)."""
+        k, rt = self.rt.k, self.rt
+        g = ctx.groups[cache.group]
+        T, r, R = x.shape[0], self.kv_rank, self.rot
+        q = self.uq.forward(x)                                                   # [T, H * (dim + R)]
+        down = self.down.forward(x, out_dtype=torch.float32) if self.down is not None else None
+        store = cache.writable and not self.share_kv
+        q_lat = torch.empty((T, self.nh * self.row), dtype=torch.float32, device=x.device)
+        # the latent's norm and the rotation of the shared key part into the token's cache row; the queries'
+        # rotated parts into the places behind their latent parts
+        k.latent_rope_prepare(q, down[:, :self.row] if store else None, ctx.positions, self.inv_freq, self.c_norm, self.eps,
+                              g.slot_mapping if store else None, cache.kv if store else None, q_lat, self.nh, self.hd, R, r,
+                              ctx.status)
+        k.head_linear(q, self.uk_t, torch.float32, x_head_stride=self.hd + R, out=q_lat, out_head_stride=self.row)
+        opts = dict(sinks=self.sinks) if self.sinks is not None else {}
+        wide = getattr(k, "wide_attention_takes", None)
+        if wide is not None and wide(q_lat, cache.kv, self.row, self.row, None):
+            o_lat = k.paged_attention_wide(q_lat, cache.kv, ctx, g, self.nh, 1, self.row, self.scale, 0.0, self.window, **opts)
+        else:
+            o_lat = k.paged_attention_general(q_lat, cache.kv, ctx, g, self.nh, 1, self.row, self.row, self.scale,
+                                              0.0, self.window, g.page_size, values_are_keys=True, **opts)
+        heads = k.head_linear(o_lat, self.uv, rt.dtype, x_head_stride=self.row)  # [T, H * vdim]
+        if self.has_gate:
+            at = 0 if self.share_kv else self.row
+            k.sigmoid_gate(heads, down[:, at:], self.gate_group)
+        return self.o.forward(heads)
 
     def forward(self, x, ctx, cache):
+        if self.direct:
+            return self.forward_direct(x, ctx, cache)
         k, rt = self.rt.k, self.rt
         g = ctx.groups[cache.group]
         down = self.down.forward(x, out_dtype=torch.float32)

@@ -8,22 +8,27 @@ from .linear import Linear
 
 
 class SwiGLU(FeedForward):
-    """down(silu(gate(x)) * up(x)), silu(g) = g * sigmoid(g) in 32-bit (tamnd/fastmlx
-    compute/models/llama.go:426-428, compute/models/qwen3_forward.go:229-239).  gate and
-    up run as one product whose output is [gate | up]."""
+    """down(act(gate(x)) * up(x)) with act = silu, silu(g) = g * sigmoid(g) in 32-bit (tamnd/fastmlx
+    compute/models/llama.go:426-428, compute/models/qwen3_forward.go:229-239), or, with
+    `activation="gelu_tanh"`, the tanh form of gelu.  gate and up run as one product whose output is [gate | up].
+    The suffixes complete the tensors' names."""
 
     BLOCK = 128          # gate and up rows alternate in blocks of this many when the width allows
 
     def __init__(self, width: int, intermediate: int, name: str, bias: bool = False,
-                 proj_names=("gate_proj", "up_proj", "down_proj")):
-        self.width, self.intermediate = int(width), int(intermediate)
+                 proj_names=("gate_proj", "up_proj", "down_proj"), activation: str = "silu",
+                 weight_suffix: str = ".weight", bias_suffix: str = ".bias"):
+        if activation not in ("silu", "gelu_tanh"):
+            raise ValueError(f"unknown gate activation {activation!r}")
+        self.width, self.intermediate, self.activation = int(width), int(intermediate), activation
         g, u, d = (f"{name}.{p}" for p in proj_names)
         # In blocks, a 256-wide tile of the product holds 128 gates and their 128 ups: the
-        # tensor-core kernel then applies SiLU-and-multiply in its epilogue and the [T, 2I]
+        # tensor-core kernel then applies the activation and the multiplication in its epilogue and the [T, 2I]
         # intermediate is never written.
         self.block = self.BLOCK if intermediate % self.BLOCK == 0 else 0
-        self.gate_up = Linear(width, [(g, intermediate), (u, intermediate)], bias, interleave=self.block)
-        self.down = Linear(intermediate, [(d, width)], bias)
+        self.gate_up = Linear(width, [(g, intermediate), (u, intermediate)], bias, interleave=self.block,
+                              weight_suffix=weight_suffix, bias_suffix=bias_suffix)
+        self.down = Linear(intermediate, [(d, width)], bias, weight_suffix=weight_suffix, bias_suffix=bias_suffix)
 
     def children(self):
         return (self.gate_up, self.down)
@@ -31,6 +36,15 @@ class SwiGLU(FeedForward):
     def forward(self, x, ctx):
         k, w = self.rt.k, self.gate_up.weight
         fused = self.block and self.gate_up.bias is None and hasattr(k, "can_tc")
+        if self.activation != "silu":
+            epi = getattr(k, "EPI_GELU_MUL", None)
+            if fused and epi is not None and k.can_tc(x, w, None, x.dtype, epi):
+                act = k.gemm_tcgen05(x, w, ctx.status if ctx is not None else None, epilogue=epi)
+            elif fused and epi is not None and self.block % 16 == 0 and k.can_gemv(x, w):
+                act = k.gemv(x, w, block=self.block, act=self.activation)
+            else:
+                act = k.act_mul(self.gate_up.forward(x), self.activation, self.block or None)
+            return self.down.forward(act)
         if fused and k.can_tc(x, w, None, x.dtype, k.EPI_SILU_MUL):
             # prompt portions: a 256-wide tile holds 128 gates and their ups, SiLU-mul in the epilogue
             act = k.gemm_tcgen05(x, w, ctx.status if ctx is not None else None, epilogue=k.EPI_SILU_MUL)
@@ -42,7 +56,9 @@ class SwiGLU(FeedForward):
         return self.down.forward(act)
 
     def emit(self, b, x):
-        from ..engine.native import OP_GATE_UP, _dt
+        from ..engine.native import NotNative, OP_GATE_UP, _dt
+        if self.activation != "silu":
+            raise NotNative("the native executor's gate/up operation applies SiLU")
         act = b.reg(self.intermediate)
         both = b.reg(2 * self.intermediate)              # gate and up side by side, where no kernel fuses SiLU-mul in
         w = self.gate_up.weight

@@ -37,6 +37,8 @@ class Model(Part):
             if run.cache_from is not None:
                 if not 0 <= run.cache_from < pos or self.schedule[run.cache_from].cache_from is not None:
                     raise ValueError(f"schedule[{pos}] must read the cache of an earlier entry that owns one")
+        # an embedding with per-request state of its own has a state slot behind the schedule's entries
+        self.embed_entry = len(self.schedule) if embed.state_spec() is not None else None
         self.drop = tuple(drop)
         self.vocab_size = int(vocab_size if vocab_size is not None else embed.vocab)
         self.max_positions = int(max_positions)
@@ -54,13 +56,16 @@ class Model(Part):
             layer = self.layers[run.layer]
             kv = layer.cache_spec() if run.cache_from is None else None
             out.append((kv, layer.state_spec(), run.cache_from))
+        if self.embed_entry is not None:
+            out.append((None, self.embed.state_spec(), None))
         return out
 
     @property
     def graph_safe(self) -> bool:
         """May a decode step of this model be captured in a CUDA graph?"""
         return all(getattr(layer, "supports_cuda_graph", False) for layer in self.layers) and \
-            bool(getattr(self.stream_encoding, "supports_cuda_graph", True))
+            bool(getattr(self.stream_encoding, "supports_cuda_graph", True)) and \
+            (self.embed_entry is None or bool(getattr(self.embed, "supports_cuda_graph", False)))
 
     # ---- weights
     def check_weights(self, tensors: dict[str, torch.Tensor]) -> dict[str, torch.Tensor]:
@@ -95,11 +100,16 @@ class Model(Part):
     def forward(self, ctx, greedy: bool = False) -> torch.Tensor:
         """Logits [len(ctx.logit_rows), vocab] in 32-bit for the batch that `ctx` describes;
         `greedy`: each wanted row's greedy choice instead, int32 [len(ctx.logit_rows)]."""
-        delta = self.embed.forward(ctx.tokens, ctx)
+        if self.embed_entry is not None:
+            delta = self.embed.forward(ctx.tokens, ctx, ctx.caches[self.embed_entry])
+        else:
+            delta = self.embed.forward(ctx.tokens, ctx)
         if self.stream_encoding is not None:
             delta = self.stream_encoding.forward(delta, ctx)
         ctx.scratch["embedding"] = delta              # a layer may read the embeddings again (the entry of a loop)
         residual = None
+        if getattr(self.embed, "starts_stream", False) and delta.dtype == torch.float32 and self.rt.dtype != torch.float32:
+            delta, residual = None, delta             # the embedding's output is the 32-bit stream itself
         for pos, run in enumerate(self.schedule):
             delta, residual = self.layers[run.layer].forward(delta, residual, ctx, ctx.caches[pos])
         k = self.rt.k
@@ -116,6 +126,8 @@ class Model(Part):
         """The step as a program of the native executor (engine/native.py): what `forward` does,
         said once.  Raises NotNative where a part has no `emit`."""
         from ..engine.native import NotNative, OP_GATHER_ROWS
+        if self.embed_entry is not None:
+            raise NotNative("an embedding with per-request state runs in Python only")
         for part in (self.embed, self.final_norm, self.head, *self.layers):
             if not hasattr(part, "emit") and not hasattr(part, "emit_after"):
                 raise NotNative(f"{type(part).__name__} runs in Python only")

@@ -190,19 +190,28 @@ def _rotate(heads, positions, inv_freq, rotary_dim, traditional):
 
 
 def qk_prepare(qkv, positions, inv_freq, rotary_dim, traditional, norm_eps, slot_mapping, kv, nh, nkv, hd, vd, status,
-               bias=None, q_weight=None, k_weight=None, norm_first=False):
+               bias=None, q_weight=None, k_weight=None, norm_first=False, whole=False, values_from_keys=False):
     T = qkv.shape[0]
     n_qk = (nh + nkv) * hd
-    row = qkv[:, :n_qk + nkv * vd].to(F64)
+    row = qkv[:, :n_qk + (0 if values_from_keys else nkv * vd)].to(F64)
     if bias is not None:
         row = row + bias.to(F64)
+    if values_from_keys:                       # a token's values are its keys as they were projected
+        row = torch.cat([row, row[:, nh * hd:n_qk]], 1)
     heads = row[:, :n_qk].reshape(T, nh + nkv, hd)
     w = torch.ones(nh + nkv, hd, dtype=F64)
     if q_weight is not None:
-        w[:nh], w[nh:] = q_weight.to(F64), k_weight.to(F64)
+        w[:nh], w[nh:] = q_weight.to(F64).reshape(-1, hd), k_weight.to(F64).reshape(-1, hd)
 
     def norm(h):
-        return h if norm_eps is None else h / torch.sqrt((h * h).mean(-1, keepdim=True) + norm_eps) * w
+        if norm_eps is None:
+            return h
+        if whole:                              # q and k each over the whole projection, all heads at once
+            ms = torch.cat([(h[:, :nh] ** 2).mean((1, 2), keepdim=True).expand(T, nh, 1),
+                            (h[:, nh:] ** 2).mean((1, 2), keepdim=True).expand(T, nkv, 1)], 1) if nkv else \
+                (h ** 2).mean((1, 2), keepdim=True)
+            return h / torch.sqrt(ms + norm_eps) * w
+        return h / torch.sqrt((h * h).mean(-1, keepdim=True) + norm_eps) * w
 
     heads = _rotate(norm(heads), positions, inv_freq, rotary_dim, traditional) if norm_first \
         else norm(_rotate(heads, positions, inv_freq, rotary_dim, traditional))
@@ -227,7 +236,7 @@ def qk_prepare(qkv, positions, inv_freq, rotary_dim, traditional, norm_eps, slot
 
 
 def paged_attention_general(q, kv, ctx, group, nh, nkv, hd, vd, scale, softcap, window, page_size, out=None,
-                            keep_first=0, values_are_keys=False, gate=None):
+                            keep_first=0, values_are_keys=False, gate=None, chunk=0, sinks=None, gate_group=1):
     T = q.shape[0]
     flat = kv.reshape(-1)
     res = torch.zeros(T, nh * vd, dtype=F64)
@@ -239,6 +248,8 @@ def paged_attention_general(q, kv, ctx, group, nh, nkv, hd, vd, scale, softcap, 
             continue
         bt = group.block_tables[int(ctx.token_row[t])]
         lo = max(0, pos - window + 1) if window > 0 else 0
+        if chunk > 0:
+            lo = pos - pos % chunk
         js = torch.tensor([j for j in range(pos + 1) if j >= lo or j < keep_first])
         pages = bt[(js // page_size).long()].long()
         if (pages < 0).any():
@@ -256,9 +267,15 @@ def paged_attention_general(q, kv, ctx, group, nh, nkv, hd, vd, scale, softcap, 
                 s = (K @ q[t, h * hd:(h + 1) * hd].to(F64)) * scale
                 if softcap and softcap > 0:
                     s = softcap * torch.tanh(s / softcap)
-                res[t, h * vd:(h + 1) * vd] = torch.softmax(s, 0) @ V
+                if sinks is not None:          # one more term in the denominator, with no value
+                    sk = sinks[h].to(F64)
+                    m = torch.maximum(s.max(), sk)
+                    e = torch.exp(s - m)
+                    res[t, h * vd:(h + 1) * vd] = (e / (e.sum() + torch.exp(sk - m))) @ V
+                else:
+                    res[t, h * vd:(h + 1) * vd] = torch.softmax(s, 0) @ V
     if gate is not None:
-        res = res * torch.sigmoid(gate.to(F64))
+        res = res * torch.sigmoid(gate.to(F64)).repeat_interleave(gate_group, dim=1)
     res = res.to(kv.dtype)
     if out is not None:
         out.copy_(res)
@@ -355,7 +372,137 @@ def moe_expert_act(gu, weights, E, ff, limit, limit_shared=0.0, out=None, block=
     return y
 
 
-def head_linear(x, w, out_dtype):
+def head_linear(x, w, out_dtype, x_head_stride=None, out=None, out_head_stride=None):
     H, N, K = w.shape
     T = x.shape[0]
-    return torch.einsum("thk,hnk->thn", x.reshape(T, H, K).to(F64), w.to(F64)).reshape(T, H * N).to(out_dtype)
+    xs = x_head_stride or K
+    xh = x.reshape(T, H, xs)[:, :, :K]
+    res = torch.einsum("thk,hnk->thn", xh.to(F64), w.to(F64))
+    if out is None:
+        return res.reshape(T, H * N).to(out_dtype)
+    out.view(T, H, out_head_stride or N)[:, :, :N] = res.to(out.dtype)
+    return out
+
+
+# ----------------------------------------------------------------------------- bigram embedding, rotated latents, state space
+def embed_bigram(ids, table, bigram, ctx, state, buckets, mul_prev, mul_cur):
+    T = ids.shape[0]
+    out = torch.zeros(T, table.shape[1], dtype=torch.float32)
+    last = {}
+    for t in range(T):
+        r = int(ctx.token_row[t])
+        slot, pos = int(ctx.row_slot[r]), int(ctx.positions[t])
+        if slot < 0 or pos < 0:
+            continue
+        tok = int(ids[t])
+        if not 0 <= tok < table.shape[0]:
+            ctx.status[0] = 1
+            continue
+        first = t == int(ctx.row_start[r])
+        prev = int(state[slot, 0]) if first else int(ids[t - 1])
+        row = buckets if pos == 0 else (prev * mul_prev + tok * mul_cur) % buckets
+        out[t] = (table[tok].to(F64) + bigram[row].to(F64)).to(torch.float32)
+        last[slot] = tok
+    for slot, tok in last.items():
+        state[slot, 0] = tok
+    return out
+
+
+def latent_rope_prepare(q, dkv, positions, inv_freq, norm_w, eps, slot_mapping, kv, q_lat, H, D, R, r, status):
+    T = q.shape[0]
+    row = r + R
+    if R:
+        qr = q.reshape(T, H, D + R)[:, :, D:].to(F64)
+        q_lat.view(T, H, row)[:, :, r:] = _rotate(qr, positions, inv_freq, R, False).to(q_lat.dtype)
+    if kv is None or dkv is None:
+        return
+    c = dkv[:, :r].to(F64)
+    c = c / torch.sqrt((c * c).mean(-1, keepdim=True) + eps) * norm_w.to(F64)
+    both = c
+    if R:
+        kr = _rotate(dkv[:, r:row].to(F64).reshape(T, 1, R), positions, inv_freq, R, False).reshape(T, R)
+        both = torch.cat([c, kr], 1)
+    flat = kv.view(-1, row)
+    for t in range(T):
+        s = int(slot_mapping[t])
+        if s < 0:
+            continue
+        if s >= flat.shape[0]:
+            status[0] = 2
+            continue
+        flat[s] = both[t].to(kv.dtype)
+
+
+def _silu(z):
+    return z * torch.sigmoid(z)
+
+
+def ssm_prepare(proj, conv_w, conv_b, a_log, dt_bias, ctx, state, conv_off, H, G, N, P, taps):
+    T = proj.shape[0]
+    inner = H * P
+    C = inner + 2 * G * N
+    xbc = torch.zeros(T, C, dtype=torch.float32)
+    dd = torch.zeros(T, 2 * H, dtype=torch.float32)
+    w, b = conv_w.to(F64), conv_b.to(F64)
+    for r in range(ctx.R):
+        slot = int(ctx.row_slot[r])
+        a, e = int(ctx.row_start[r]), int(ctx.row_start[r + 1])
+        if slot < 0 or e <= a:
+            continue
+        hist = state[slot, conv_off:conv_off + (taps - 1) * C].to(F64).reshape(taps - 1, C)
+        u = torch.cat([hist, proj[a:e, inner:inner + C].to(F64)], 0)            # [taps-1 + n, C]
+        for t in range(e - a):
+            xbc[a + t] = _silu((u[t:t + taps] * w.t()).sum(0) + b).to(torch.float32)
+        state[slot, conv_off:conv_off + (taps - 1) * C] = u[u.shape[0] - (taps - 1):].reshape(-1).to(torch.float32)
+        dt = torch.nn.functional.softplus(proj[a:e, inner + C:inner + C + H].to(F64) + dt_bias.to(F64), threshold=40.0)
+        dd[a:e, :H] = dt.to(torch.float32)
+        dd[a:e, H:] = torch.exp(-torch.exp(a_log.to(F64)) * dt).to(torch.float32)
+    return xbc, dd
+
+
+def ssm_scan(xbc, dd, d_skip, ctx, state, H, G, N, P):
+    T = xbc.shape[0]
+    inner = H * P
+    y = torch.zeros(T, inner, dtype=torch.float32)
+    per = H // G
+    for r in range(ctx.R):
+        slot = int(ctx.row_slot[r])
+        a, e = int(ctx.row_start[r]), int(ctx.row_start[r + 1])
+        if slot < 0 or e <= a:
+            continue
+        S = state[slot, :H * P * N].to(F64).reshape(H, P, N)                   # S^T of every head
+        for t in range(a, e):
+            x = xbc[t, :inner].to(F64).reshape(H, P)
+            B = xbc[t, inner:inner + G * N].to(F64).reshape(G, N).repeat_interleave(per, 0)
+            Cm = xbc[t, inner + G * N:].to(F64).reshape(G, N).repeat_interleave(per, 0)
+            dt, decay = dd[t, :H].to(F64), dd[t, H:].to(F64)
+            S = decay[:, None, None] * S + dt[:, None, None] * x[:, :, None] * B[:, None, :]
+            y[t] = ((S * Cm[:, None, :]).sum(-1) + d_skip.to(F64)[:, None] * x).reshape(-1).to(torch.float32)
+        state[slot, :H * P * N] = S.reshape(-1).to(torch.float32)
+    return y
+
+
+def gated_group_rmsnorm(y, z, weight, eps, groups, out_dtype, out=None):
+    T, n = y.shape
+    v = y.to(F64) * _silu(z.to(F64))
+    v = v.reshape(T, groups, n // groups)
+    v = (v / torch.sqrt((v * v).mean(-1, keepdim=True) + eps)).reshape(T, n) * weight.to(F64)
+    res = v.to(out_dtype)
+    if out is not None:
+        out.copy_(res)
+        return out
+    return res
+
+
+def act_mul(gate_up, kind, block=None):
+    inter = gate_up.shape[1] // 2
+    b = block or inter
+    v = gate_up.reshape(gate_up.shape[0], inter // b, 2, b).to(F64)
+    g, u = v[:, :, 0, :].reshape(-1, inter), v[:, :, 1, :].reshape(-1, inter)
+    if kind == "silu":
+        a = _silu(g)
+    elif kind == "gelu_tanh":
+        a = 0.5 * g * (1.0 + torch.tanh(0.7978845608028654 * (g + 0.044715 * g ** 3)))
+    else:
+        raise ValueError(kind)
+    return (a * u).to(gate_up.dtype)
