@@ -21,6 +21,12 @@
 // [nkv, page_size, hd], and the values are those same vectors (vd = hd): attention over a cached
 // latent.  `gate` (32-bit, [T, nh * vd] in rows of gate_stride): the output is multiplied element by
 // element with sigmoid(gate).
+//
+// And three more.  `chunk` c > 0 (instead of a window): a query at position p sees the keys from p - p % c on, the
+// run of c positions it lies in, runs counted from position 0.  `sinks` (32-bit, one number per query head): the
+// softmax's denominator has one more term exp(sink) that has no key and no value and is not scaled or capped
+// (a sink of 0 adds one).  `gate_group` g > 1: the gate holds one value per g output elements ([T, nh * vd / g];
+// g = vd: one per head).
 #include <math.h>
 #include "common.cuh"
 
@@ -35,7 +41,8 @@ paged_attention_simple_kernel(const TQ* __restrict__ q, long long q_stride, cons
                               const int* __restrict__ positions, T* __restrict__ out, long long out_stride, int n_tokens,
                               int nh, int nkv, int hd, int vd, int page_size, long long num_pages, float scale,
                               float softcap, int window, int R, int* status, int keep_first, int values_are_keys,
-                              const float* gate, long long gate_stride) {
+                              const float* gate, long long gate_stride, int chunk, const float* __restrict__ sinks,
+                              int gate_group) {
   extern __shared__ float smem[];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const long long w = (long long)blockIdx.x * WARPS + warp;
@@ -56,7 +63,7 @@ paged_attention_simple_kernel(const TQ* __restrict__ q, long long q_stride, cons
   }
   const int pos = positions[t];
   const int* bt = block_tables + (long long)row * bt_stride;
-  const int lo = window > 0 ? max(0, pos - window + 1) : 0;
+  const int lo = window > 0 ? max(0, pos - window + 1) : (chunk > 0 && pos > 0 ? pos - pos % chunk : 0);
   const long long plane = values_are_keys ? 0 : (long long)nkv * page_size * hd;     // a page's keys, then its values
   const long long page_elems = (long long)nkv * page_size * (values_are_keys ? hd : hd + vd);
   // positions below `kept` are seen although the window has passed them
@@ -110,13 +117,21 @@ paged_attention_simple_kernel(const TQ* __restrict__ q, long long q_stride, cons
     }
     m = m_new;
   }
+  if (sinks != nullptr && m != -INFINITY) {      // the term without a value: the sums move to the larger maximum
+    const float sk = sinks[h];
+    const float m_new = fmaxf(m, sk);
+    const float alpha = expf(m - m_new);
+    l = l * alpha + expf(sk - m_new);
+#pragma unroll
+    for (int i = 0; i < MAX_HD / 32; ++i) acc[i] *= alpha;
+  }
   const float inv = l > 0.f ? 1.0f / l : 0.f;
 #pragma unroll
   for (int i = 0; i < MAX_HD / 32; ++i) {
     const int e = lane + 32 * i;
     if (e < vd) {
       float o = acc[i] * inv;
-      if (gate != nullptr) o *= 1.0f / (1.0f + expf(-gate[(long long)t * gate_stride + (long long)h * vd + e]));
+      if (gate != nullptr) o *= 1.0f / (1.0f + expf(-gate[(long long)t * gate_stride + ((long long)h * vd + e) / gate_group]));
       op[e] = from_f<T>(o);
     }
   }
@@ -125,15 +140,17 @@ paged_attention_simple_kernel(const TQ* __restrict__ q, long long q_stride, cons
 
 // q_dtype: the queries' type (FMX_F32 beside a bfloat16 cache, or the cache's own); dtype: the type of the
 // cache and of the output; hd / vd: head sizes of keys and values; softcap <= 0: scores are not capped.
-// keep_first, values_are_keys, gate: see the head of the file (0, 0, null: none of them).
-FMX_EXPORT int fmx_paged_attention_masked(const void* q, long long q_stride, int q_dtype, const void* kv,
+// keep_first, values_are_keys, gate, chunk, sinks, gate_group: see the head of the file (0, 0, null, 0, null, 1: none of them).
+FMX_EXPORT int fmx_paged_attention_masked_ex(const void* q, long long q_stride, int q_dtype, const void* kv,
                                           const int* block_tables, int bt_stride, const int* token_row,
                                           const int* positions, void* out, long long out_stride, int n_tokens, int nh,
                                           int nkv, int hd, int vd, int page_size, long long num_pages, float scale,
                                           float softcap, int window, int R, int dtype, int* status, int keep_first,
-                                          int values_are_keys, const float* gate, long long gate_stride,
-                                          cudaStream_t stream) {
+                                          int values_are_keys, const float* gate, long long gate_stride, int chunk,
+                                          const float* sinks, int gate_group, cudaStream_t stream) {
   if (n_tokens == 0) return 0;
+  if (chunk < 0 || (chunk > 0 && window > 0) || gate_group < 1 || (gate != nullptr && (vd % gate_group) && gate_group != 1))
+    return fmx_fail("fmx_paged_attention_general: bad chunk %d beside window %d, or gate group %d", chunk, window, gate_group);
   if (n_tokens < 0 || nh <= 0 || nkv <= 0 || nh % nkv || hd <= 0 || vd <= 0 || page_size <= 0)
     return fmx_fail("fmx_paged_attention_general: bad sizes T=%d nh=%d nkv=%d hd=%d vd=%d page=%d", n_tokens, nh, nkv, hd,
                     vd, page_size);
@@ -147,9 +164,9 @@ FMX_EXPORT int fmx_paged_attention_masked(const void* q, long long q_stride, int
   paged_attention_simple_kernel<TQ, T><<<(unsigned)grid, WARPS * 32, smem, stream>>>(                                 \
       (const TQ*)q, q_stride, (const T*)kv, block_tables, bt_stride, token_row, positions, (T*)out, out_stride, n_tokens, \
       nh, nkv, hd, vd, page_size, num_pages, scale, softcap, window, R, status, keep_first, values_are_keys, gate,        \
-      gate_stride)
+      gate_stride, chunk, sinks, gate_group)
   if (values_are_keys && hd != vd) return fmx_fail("fmx_paged_attention_general: values that are the keys have the keys' width");
-  if (keep_first < 0 || (gate != nullptr && gate_stride < (long long)nh * vd))
+  if (keep_first < 0 || (gate != nullptr && gate_stride < (long long)nh * vd / gate_group))
     return fmx_fail("fmx_paged_attention_general: bad keep_first %d or gate rows too narrow", keep_first);
   if (dtype == FMX_F32 && q_dtype == FMX_F32)
     FMX_ATTN_SIMPLE(float, float);
@@ -162,6 +179,18 @@ FMX_EXPORT int fmx_paged_attention_masked(const void* q, long long q_stride, int
 #undef FMX_ATTN_SIMPLE
   FMX_LAUNCH_CHECK();
   return 0;
+}
+
+FMX_EXPORT int fmx_paged_attention_masked(const void* q, long long q_stride, int q_dtype, const void* kv,
+                                          const int* block_tables, int bt_stride, const int* token_row,
+                                          const int* positions, void* out, long long out_stride, int n_tokens, int nh,
+                                          int nkv, int hd, int vd, int page_size, long long num_pages, float scale,
+                                          float softcap, int window, int R, int dtype, int* status, int keep_first,
+                                          int values_are_keys, const float* gate, long long gate_stride,
+                                          cudaStream_t stream) {
+  return fmx_paged_attention_masked_ex(q, q_stride, q_dtype, kv, block_tables, bt_stride, token_row, positions, out, out_stride,
+                                       n_tokens, nh, nkv, hd, vd, page_size, num_pages, scale, softcap, window, R, dtype, status,
+                                       keep_first, values_are_keys, gate, gate_stride, 0, nullptr, 1, stream);
 }
 
 FMX_EXPORT int fmx_paged_attention_general(const void* q, long long q_stride, int q_dtype, const void* kv,

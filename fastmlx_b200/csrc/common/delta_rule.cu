@@ -24,10 +24,9 @@
 #include <math.h>
 #include "common.cuh"
 
-namespace {
-constexpr int MAX_TAPS = 16;
+#include "conv_state.cuh"
 
-__device__ __forceinline__ float silu_f(float x) { return x / (1.0f + expf(-x)); }
+namespace {
 
 // proj [T, stride]: q (G*D) | k (G*D) | v (H*Dv) | ... ; ab [T, ab_stride] 32-bit: b (H) | a (H).
 // out_qkv [T, C] 32-bit; out_gb [T, 2H]: decay | beta.
@@ -85,33 +84,6 @@ delta_prepare_kernel(const T* proj, long long stride, const float* ab, long long
     og[h] = expf(-expf(a_log[h]) * sp);
     og[H + h] = 1.0f / (1.0f + expf(-b));
   }
-}
-
-// One thread per (request, channel): the last taps-1 inputs of the request's portion (reaching back into the old
-// state where the portion is shorter) become the new state.
-template <typename T>
-__global__ void conv_state_update_kernel(const T* proj, long long stride, const int* row_start, const int* row_slot,
-                                         float* state, long long slot_stride, long long conv_off, int C, int taps,
-                                         int max_slots) {
-  pdl_wait();
-  pdl_trigger();
-  const int r = blockIdx.y;
-  const int c = blockIdx.x * blockDim.x + threadIdx.x;
-  const int slot = row_slot[r];
-  if (c >= C || slot < 0 || slot >= max_slots) return;
-  const int first = row_start[r], n = row_start[r + 1] - first;
-  float* cs = state + (long long)slot * slot_stride + conv_off;
-  float keep[MAX_TAPS];
-#pragma unroll
-  for (int j = 0; j < MAX_TAPS; ++j) {
-    if (j < taps - 1) {
-      const int p = n - (taps - 1) + j;
-      keep[j] = p >= 0 ? to_f(proj[(long long)(first + p) * stride + c]) : cs[(long long)(taps - 1 + p) * C + c];
-    }
-  }
-#pragma unroll
-  for (int j = 0; j < MAX_TAPS; ++j)
-    if (j < taps - 1) cs[(long long)j * C + c] = keep[j];
 }
 
 // grid (ceil(Dv / COLS), H, R), 128 threads: COLS = 128 / L columns of S, L adjacent lanes each; lane `sub` of a

@@ -235,11 +235,16 @@ FMX_EXPORT int fmx_add_rmsnorm(const void* x, void* residual, const float* w, vo
   return 0;
 }
 
-// out[t, i] = silu(gate_i) * up_i, silu(g) = g / (1 + exp(-g)), in 32-bit.  A row of gu holds
-// 2 I values in blocks: `blk` gates, then their `blk` ups, and so on; blk = I is the plain
-// layout [all gates | all ups].
-template <typename T>
-__global__ void silu_mul_kernel(const T* __restrict__ gu, T* __restrict__ out, long long rows, int I, int blk) {
+// out[t, i] = act(gate_i) * up_i in 32-bit, act = silu (g / (1 + exp(-g)), KIND 2) or the tanh form of gelu
+// (0.5 g (1 + tanh(sqrt(2/pi) (g + 0.044715 g^3))), KIND 1).  A row of gu holds 2 I values in blocks: `blk` gates,
+// then their `blk` ups, and so on; blk = I is the plain layout [all gates | all ups].
+template <int KIND> __device__ __forceinline__ float gate_act(float g) {
+  if (KIND == 1) return 0.5f * g * (1.0f + tanhf(0.7978845608028654f * (g + 0.044715f * g * g * g)));
+  return g / (1.0f + expf(-g));
+}
+
+template <typename T, int KIND>
+__global__ void act_mul_kernel(const T* __restrict__ gu, T* __restrict__ out, long long rows, int I, int blk) {
   const long long n = rows * I;
   for (long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x; idx < n;
        idx += (long long)gridDim.x * blockDim.x) {
@@ -248,12 +253,13 @@ __global__ void silu_mul_kernel(const T* __restrict__ gu, T* __restrict__ out, l
     const int b = i / blk, j = i - b * blk;
     const float g = to_f(gu[t * 2 * I + (long long)b * 2 * blk + j]);
     const float u = to_f(gu[t * 2 * I + (long long)b * 2 * blk + blk + j]);
-    out[idx] = from_f<T>(g / (1.0f + expf(-g)) * u);
+    out[idx] = from_f<T>(gate_act<KIND>(g) * u);
   }
 }
 
 // bfloat16 with I a multiple of 8: eight elements per thread, 16-byte loads and stores.
-__global__ void silu_mul_bf16_vec_kernel(const bf16* gu, bf16* out, int I, int blk) {
+template <int KIND>
+__global__ void act_mul_bf16_vec_kernel(const bf16* gu, bf16* out, int I, int blk) {
   pdl_wait();
   pdl_trigger();
   const long long t = blockIdx.y;
@@ -270,34 +276,46 @@ __global__ void silu_mul_bf16_vec_kernel(const bf16* gu, bf16* out, int I, int b
 #pragma unroll
     for (int e = 0; e < 4; ++e) {
       const float2 g = __bfloat1622float2(g2[e]), u = __bfloat1622float2(u2[e]);
-      r2[e] = __floats2bfloat162_rn(g.x / (1.0f + expf(-g.x)) * u.x, g.y / (1.0f + expf(-g.y)) * u.y);
+      r2[e] = __floats2bfloat162_rn(gate_act<KIND>(g.x) * u.x, gate_act<KIND>(g.y) * u.y);
     }
     op[i] = r;
   }
 }
 
-FMX_EXPORT int fmx_silu_mul(const void* gu, void* out, int rows, int I, int blk, int dtype, cudaStream_t stream) {
-  if (rows == 0) return 0;
-  if (rows < 0 || I <= 0) return fmx_fail("fmx_silu_mul: bad sizes rows=%d I=%d", rows, I);
-  if (blk <= 0 || I % blk) return fmx_fail("fmx_silu_mul: %d is no multiple of the block size %d", I, blk);
+template <int KIND>
+static int act_mul_launch(const void* gu, void* out, int rows, int I, int blk, int dtype, cudaStream_t stream) {
   const long long n = (long long)rows * I;
   const int block = 256;
   const long long cap = (long long)fmx_num_sms() * 16;
   const int grid = (int)((n + block - 1) / block < cap ? (n + block - 1) / block : cap);
   if (dtype == FMX_F32)
-    silu_mul_kernel<float><<<grid, block, 0, stream>>>((const float*)gu, (float*)out, rows, I, blk);
+    act_mul_kernel<float, KIND><<<grid, block, 0, stream>>>((const float*)gu, (float*)out, rows, I, blk);
   else if (dtype == FMX_BF16) {
     if (I % 8 == 0 && blk % 8 == 0 && aligned16(gu) && aligned16(out) && rows <= 65535) {
       const int bx = (I / 8 + block - 1) / block;
-      fmx_launch(silu_mul_bf16_vec_kernel, dim3(bx < 64 ? bx : 64, rows), dim3(block), 0, stream, (const bf16*)gu,
+      fmx_launch(act_mul_bf16_vec_kernel<KIND>, dim3(bx < 64 ? bx : 64, rows), dim3(block), 0, stream, (const bf16*)gu,
                  (bf16*)out, I, blk);
     } else {
-      silu_mul_kernel<bf16><<<grid, block, 0, stream>>>((const bf16*)gu, (bf16*)out, rows, I, blk);
+      act_mul_kernel<bf16, KIND><<<grid, block, 0, stream>>>((const bf16*)gu, (bf16*)out, rows, I, blk);
     }
   } else
-    return fmx_fail("fmx_silu_mul: unknown dtype %d", dtype);
+    return fmx_fail("fmx_act_mul: unknown dtype %d", dtype);
   FMX_LAUNCH_CHECK();
   return 0;
+}
+
+// kind: 1 the tanh form of gelu, 2 silu (the numbers of fmx_activation)
+FMX_EXPORT int fmx_act_mul(const void* gu, void* out, int rows, int I, int blk, int kind, int dtype, cudaStream_t stream) {
+  if (rows == 0) return 0;
+  if (rows < 0 || I <= 0) return fmx_fail("fmx_act_mul: bad sizes rows=%d I=%d", rows, I);
+  if (blk <= 0 || I % blk) return fmx_fail("fmx_act_mul: %d is no multiple of the block size %d", I, blk);
+  if (kind == 1) return act_mul_launch<1>(gu, out, rows, I, blk, dtype, stream);
+  if (kind == 2) return act_mul_launch<2>(gu, out, rows, I, blk, dtype, stream);
+  return fmx_fail("fmx_act_mul: the gate's activation is gelu (1) or silu (2), not %d", kind);
+}
+
+FMX_EXPORT int fmx_silu_mul(const void* gu, void* out, int rows, int I, int blk, int dtype, cudaStream_t stream) {
+  return fmx_act_mul(gu, out, rows, I, blk, 2, dtype, stream);
 }
 
 // out[r, :] = vec for every row: the bias laid under a library product that adds to what it finds

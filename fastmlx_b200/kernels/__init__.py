@@ -109,6 +109,17 @@ def silu_mul(gate_up: torch.Tensor, block: int | None = None) -> torch.Tensor:
     return out
 
 
+def act_mul(gate_up: torch.Tensor, kind: str, block: int | None = None) -> torch.Tensor:
+    """act(gate) * up like `silu_mul`, with act = "silu" or "gelu_tanh" (the tanh form of gelu), in 32-bit."""
+    _need_cuda(gate_up)
+    assert gate_up.dim() == 2 and gate_up.is_contiguous() and gate_up.shape[1] % 2 == 0 and kind in ("silu", "gelu_tanh")
+    rows, inter = gate_up.shape[0], gate_up.shape[1] // 2
+    out = torch.empty((rows, inter), dtype=gate_up.dtype, device=gate_up.device)
+    call("common", "fmx_act_mul", gate_up.data_ptr(), out.data_ptr(), rows, inter, int(block or inter), ACTIVATIONS[kind],
+         _dt(gate_up), _stream())
+    return out
+
+
 # ----------------------------------------------------------------------------- matrix products
 def gemm_simple(x, w, bias, out_dtype) -> torch.Tensor:
     M, K = x.shape
@@ -321,14 +332,17 @@ def paged_attention_simple(qkv, kv, ctx, group, nh, nkv, hd, scale, window) -> t
 
 
 def qk_prepare(qkv, positions, inv_freq, rotary_dim, traditional, norm_eps, slot_mapping, kv, nh, nkv, hd, vd,
-               status, bias=None, q_weight=None, k_weight=None, norm_first: bool = False) -> torch.Tensor:
+               status, bias=None, q_weight=None, k_weight=None, norm_first: bool = False, whole: bool = False,
+               values_from_keys: bool = False) -> torch.Tensor:
     """Queries and keys of qkv[T, nh*hd + nkv*hd + nkv*vd] made ready for attention: rotated over their
     first `rotary_dim` dimensions, then (norm_eps not None) each head divided by its root mean square;
     keys and values are stored at slot_mapping in pages that hold [nkv, page, hd] keys and then
     [nkv, page, vd] values.  -> the queries in 32-bit, [T, nh*hd].  qkv may be of another type than the
     cache (a product that leaves in 32-bit beside bfloat16 pages).  `bias` (32-bit, a whole row's) is added
     first; `q_weight` / `k_weight` ([hd], 32-bit) multiply the normalised heads; `norm_first` normalises
-    before the rotation instead of after it."""
+    before the rotation instead of after it.  `whole` (with `norm_first`): q and k are each divided by the root mean
+    square of their whole projection, all heads at once, and the weights are that wide ([nh*hd], [nkv*hd]);
+    `values_from_keys`: qkv holds q | k only, and a token's values are its keys as projected (vd = hd)."""
     _need_cuda(qkv, positions, inv_freq, slot_mapping, kv, bias, q_weight, k_weight)
     assert qkv.dim() == 2 and qkv.stride(1) == 1 and positions.dtype == torch.int32
     T = qkv.shape[0]
@@ -341,6 +355,14 @@ def qk_prepare(qkv, positions, inv_freq, rotary_dim, traditional, norm_eps, slot
         num_pages, page_size = 0, 1
     for v in (bias, q_weight, k_weight):
         assert v is None or (v.dtype == torch.float32 and v.is_contiguous())
+    if whole or values_from_keys:
+        assert norm_first or norm_eps is None, "the norm over the whole projection comes before the rotation"
+        call("common", "fmx_qk_prepare_whole", qkv.data_ptr(), qkv.stride(0), positions.data_ptr(), _ptr(inv_freq),
+             _ptr(slot_mapping), q.data_ptr(), _ptr(kv), T, nh, nkv if kv is not None else 0, hd, vd, int(rotary_dim),
+             int(bool(traditional)), -1.0 if norm_eps is None else float(norm_eps), page_size, num_pages, _dt(qkv),
+             _dt(kv) if kv is not None else _dt(qkv), _ptr(bias), _ptr(q_weight), _ptr(k_weight), int(bool(values_from_keys)),
+             _ptr(status), _stream())
+        return q
     call("common", "fmx_qk_prepare_ex", qkv.data_ptr(), qkv.stride(0), positions.data_ptr(), _ptr(inv_freq),
          _ptr(slot_mapping), q.data_ptr(), _ptr(kv), T, nh, nkv if kv is not None else 0, hd, vd, int(rotary_dim),
          int(bool(traditional)), -1.0 if norm_eps is None else float(norm_eps), page_size, num_pages, _dt(qkv),
@@ -350,21 +372,32 @@ def qk_prepare(qkv, positions, inv_freq, rotary_dim, traditional, norm_eps, slot
 
 
 def paged_attention_general(q, kv, ctx, group, nh, nkv, hd, vd, scale, softcap, window, page_size, out=None,
-                            keep_first: int = 0, values_are_keys: bool = False, gate=None) -> torch.Tensor:
+                            keep_first: int = 0, values_are_keys: bool = False, gate=None, chunk: int = 0, sinks=None,
+                            gate_group: int = 1) -> torch.Tensor:
     """Attention with 32-bit scores and weights, one warp per (token, head): queries q[T, nh*hd] of their own
     type over pages of [nkv, page, hd] keys and [nkv, page, vd] values; scores are capped by
     softcap * tanh(s / softcap) where softcap > 0.  `out` may be a slice of a wider buffer.  -> [T, nh*vd].
     `keep_first`: beside a window, a request's first tokens that stay visible; `values_are_keys`: pages of keys
     only, which are the values too; `gate` (32-bit [T, nh*vd], rows may be a slice): the output is multiplied
-    element by element with sigmoid(gate)."""
-    _need_cuda(q, kv, gate)
+    element by element with sigmoid(gate) (`gate_group` g > 1: one gate value per g output elements).  `chunk` c > 0
+    instead of a window: a query sees the keys of its own run of c positions, runs counted from position 0.  `sinks`
+    (32-bit [nh]): one more term exp(sink) per head in the softmax's denominator, with no value."""
+    _need_cuda(q, kv, gate, sinks)
     assert kv.is_contiguous() and q.stride(1) == 1
     T = q.shape[0]
     if out is None:
         out = torch.empty((T, nh * vd), dtype=kv.dtype, device=q.device)
     assert out.dtype == kv.dtype and out.stride(1) == 1 and out.shape == (T, nh * vd)
-    assert gate is None or (gate.dtype == torch.float32 and gate.stride(1) == 1 and gate.shape == (T, nh * vd))
+    assert gate is None or (gate.dtype == torch.float32 and gate.stride(1) == 1 and gate.shape == (T, nh * vd // gate_group))
+    assert sinks is None or (sinks.dtype == torch.float32 and sinks.is_contiguous() and sinks.numel() == nh)
     bt = group.block_tables
+    if chunk or sinks is not None or gate_group != 1:
+        call("common", "fmx_paged_attention_masked_ex", q.data_ptr(), q.stride(0), _dt(q), kv.data_ptr(), bt.data_ptr(),
+             bt.stride(0), ctx.token_row.data_ptr(), ctx.positions.data_ptr(), out.data_ptr(), out.stride(0), T, nh, nkv, hd,
+             vd, int(page_size), kv.shape[0], float(scale), float(softcap or 0.0), int(window), bt.shape[0], _dt(kv),
+             _ptr(ctx.status), int(keep_first), int(bool(values_are_keys)), _ptr(gate),
+             gate.stride(0) if gate is not None else 0, int(chunk), _ptr(sinks), int(gate_group), _stream())
+        return out
     call("common", "fmx_paged_attention_masked", q.data_ptr(), q.stride(0), _dt(q), kv.data_ptr(), bt.data_ptr(),
          bt.stride(0), ctx.token_row.data_ptr(), ctx.positions.data_ptr(), out.data_ptr(), out.stride(0), T, nh, nkv, hd, vd,
          int(page_size), kv.shape[0], float(scale), float(softcap or 0.0), int(window), bt.shape[0], _dt(kv),
@@ -502,6 +535,89 @@ def gated_rmsnorm(o, gate, weight, eps, H, Dv, out_dtype, out=None) -> torch.Ten
     assert gate.stride(1) == 1 and out.stride(1) == 1 and gate.dtype == out.dtype and o.is_contiguous()
     call("common", "fmx_gated_rmsnorm", o.data_ptr(), gate.data_ptr(), gate.stride(0), weight.data_ptr(), out.data_ptr(),
          out.stride(0), T, H, Dv, float(eps), _dt(out), _stream())
+    return out
+
+
+# ----------------------------------------------------------------------------- bigram embedding, rotated latents, state space
+def embed_bigram(ids, table, bigram, ctx, state, buckets: int, mul_prev: int, mul_cur: int) -> torch.Tensor:
+    """table[id_t] + bigram[(id_(t-1) * mul_prev + id_t * mul_cur) mod buckets] in 32-bit, [T, d]; a request's first
+    token takes row `buckets`.  `state` (int32 [slots, 1]) holds the token before a row's first token of this step and
+    is left holding the row's last one.  Rows of slot -1 or tokens at position -1 get zeros."""
+    _need_cuda(ids, table, bigram, state)
+    assert ids.dtype == torch.int32 and table.dim() == 2 and table.is_contiguous() and bigram.is_contiguous()
+    assert bigram.shape == (buckets + 1, table.shape[1]) and bigram.dtype == table.dtype
+    assert state.dtype == torch.int32 and state.is_contiguous()
+    T, d = ids.numel(), table.shape[1]
+    out = torch.empty((T, d), dtype=torch.float32, device=table.device)
+    call("common", "fmx_embed_bigram", ids.data_ptr(), table.data_ptr(), bigram.data_ptr(), ctx.positions.data_ptr(),
+         ctx.token_row.data_ptr(), ctx.row_start.data_ptr(), ctx.row_slot.data_ptr(), state.data_ptr(), state.stride(0),
+         out.data_ptr(), T, d, table.shape[0], int(buckets), int(mul_prev), int(mul_cur), ctx.R, state.shape[0], _dt(table),
+         _ptr(ctx.status), _stream())
+    return out
+
+
+def latent_rope_prepare(q, dkv, positions, inv_freq, norm_w, eps, slot_mapping, kv, q_lat, H, D, R, r, status) -> None:
+    """Latent attention with a rotated key part: a token's down-projection dkv[t, :r+R] (32-bit; rows may be a slice)
+    becomes its cache row [rmsnorm(dkv[:r]) * norm_w | dkv[r:] rotated] at slot_mapping[t] of `kv` (rows of r + R
+    values), and the rotated parts of its query heads (q[t, h, D:D+R], pairs (i, i + R/2)) go, rotated, to
+    q_lat[t, h, r:r+R] in 32-bit.  dkv / kv None: a layer that reads another's cache stores nothing."""
+    _need_cuda(q, dkv, positions, inv_freq, norm_w, slot_mapping, kv, q_lat)
+    assert q.dim() == 2 and q.stride(1) == 1 and q_lat.dtype == torch.float32 and q_lat.is_contiguous()
+    assert q_lat.shape == (q.shape[0], H * (r + R))
+    store = kv is not None and dkv is not None
+    if store:
+        assert dkv.dtype == torch.float32 and dkv.stride(1) == 1 and kv.is_contiguous() and kv.numel() % (r + R) == 0
+        assert slot_mapping.dtype == torch.int64
+    if not store and R == 0:
+        return
+    call("common", "fmx_latent_rope_prepare", q.data_ptr(), q.stride(0), _dt(q), _ptr(dkv) if store else None,
+         dkv.stride(0) if store else 0, positions.data_ptr(), _ptr(inv_freq), _ptr(norm_w) if store else None, float(eps),
+         _ptr(slot_mapping) if store else None, _ptr(kv) if store else None, kv.numel() // (r + R) if store else 0,
+         _dt(kv) if store else _dt(q), q_lat.data_ptr(), q.shape[0], H, D, R, r, _ptr(status), _stream())
+
+
+def ssm_prepare(proj, conv_w, conv_b, a_log, dt_bias, ctx, state, conv_off, H, G, N, P, taps):
+    """What a state-space recurrence takes in, from a step's projection proj[T, z (H*P) | x (H*P) | B (G*N) | C (G*N) |
+    dt (H)]: x | B | C pass a causal convolution of `taps` taps with a bias (weights conv_w[C, taps]; inputs before
+    a portion's start come from the request's state slot, which then takes the portion's last inputs) and SiLU;
+    dt = softplus(dt + dt_bias), decay = exp(-exp(A_log) dt).
+    -> (x | B | C in 32-bit [T, C], dt | decay in 32-bit [T, 2H])."""
+    _need_cuda(proj, conv_w, conv_b, a_log, dt_bias, state)
+    T = proj.shape[0]
+    C = H * P + 2 * G * N
+    assert proj.stride(1) == 1 and state.dtype == torch.float32 and state.is_contiguous()
+    assert conv_w.dtype == torch.float32 and conv_w.is_contiguous() and conv_w.shape == (C, taps) and conv_b.shape == (C,)
+    xbc = torch.empty((T, C), dtype=torch.float32, device=proj.device)
+    dd = torch.empty((T, 2 * H), dtype=torch.float32, device=proj.device)
+    call("common", "fmx_ssm_prepare", proj.data_ptr(), proj.stride(0), conv_w.data_ptr(), conv_b.data_ptr(), a_log.data_ptr(),
+         dt_bias.data_ptr(), ctx.token_row.data_ptr(), ctx.row_start.data_ptr(), ctx.row_slot.data_ptr(), state.data_ptr(),
+         state.stride(0), int(conv_off), xbc.data_ptr(), dd.data_ptr(), T, ctx.R, H, G, N, P, int(taps), state.shape[0],
+         _dt(proj), _ptr(ctx.status), _stream())
+    return xbc, dd
+
+
+def ssm_scan(xbc, dd, d_skip, ctx, state, H, G, N, P, lanes: int = 0) -> torch.Tensor:
+    """The state-space recurrence over every request's tokens of the step, in order, from and into the requests' state
+    slots (S^T per head, [H, P, N], at the head of a slot): S <- decay S + dt B x^T; y = S^T C + D x.  `lanes` (2 to 32,
+    a power of two; 0: the library's choice): lanes that share a column of S.  -> y in 32-bit, [T, H*P]."""
+    T = xbc.shape[0]
+    out = torch.empty((T, H * P), dtype=torch.float32, device=xbc.device)
+    call("common", "fmx_ssm_scan", xbc.data_ptr(), dd.data_ptr(), d_skip.data_ptr(), ctx.row_start.data_ptr(),
+         ctx.row_slot.data_ptr(), state.data_ptr(), state.stride(0), out.data_ptr(), ctx.R, H, G, N, P, state.shape[0],
+         int(lanes), _stream())
+    return out
+
+
+def gated_group_rmsnorm(y, z, weight, eps, groups, out_dtype, out=None) -> torch.Tensor:
+    """y[T, n] (32-bit) * silu(z), then each of `groups` equal parts of a row divided by its own root mean square,
+    times weight[n]; z and out may be slices of wider buffers."""
+    T, n = y.shape
+    if out is None:
+        out = torch.empty((T, n), dtype=out_dtype, device=y.device)
+    assert z.stride(1) == 1 and out.stride(1) == 1 and z.dtype == out.dtype and y.is_contiguous() and n % groups == 0
+    assert z.shape == (T, n) and weight.dtype == torch.float32 and weight.numel() == n
+    call("common", "fmx_gated_group_rmsnorm", y.data_ptr(), z.data_ptr(), z.stride(0), weight.data_ptr(), out.data_ptr(),
+         out.stride(0), T, int(groups), n // groups, float(eps), _dt(out), _stream())
     return out
 
 
@@ -700,28 +816,41 @@ def moe_combine(pair_out, plan, shared, T: int, top: int, out_dtype) -> torch.Te
     return out
 
 
-def head_linear(x, w, out_dtype) -> torch.Tensor:
+def head_linear(x, w, out_dtype, x_head_stride: int | None = None, out=None, out_head_stride: int | None = None) -> torch.Tensor:
     """A product per head: x[T, H*K] (head by head, rows may be a slice) and w[H, N, K] -> [T, H*N], out[t, h] =
     w[h] x[t, h], accumulated in 32-bit.  bfloat16 operands go to the library's batched product; 32-bit ones to
-    the fixed-order kernel, head by head."""
-    _need_cuda(x, w)
+    the fixed-order kernel, head by head.  `x_head_stride` s > K: head h's K inputs are the first K of the s values
+    at x[t, h*s]; `out` with `out_head_stride` s' > N: head h's N results go to the first N of the s' places at
+    out[t, h*s'], the rest stay as they are."""
+    _need_cuda(x, w, out)
     H, N, K = w.shape
     T = x.shape[0]
-    assert x.dim() == 2 and x.shape[1] == H * K and x.stride(1) == 1 and w.is_contiguous()
-    out = torch.empty((T, H * N), dtype=out_dtype, device=x.device)
+    xs = int(x_head_stride or K)
+    assert x.dim() == 2 and x.shape[1] >= (H - 1) * xs + K and x.stride(1) == 1 and w.is_contiguous()
+    if out is None:
+        os_ = N
+        out = torch.empty((T, H * N), dtype=out_dtype, device=x.device)
+    else:
+        os_ = int(out_head_stride or N)
+        assert out.dim() == 2 and out.shape[0] == T and out.stride(1) == 1 and out.shape[1] >= (H - 1) * os_ + N
+        out_dtype = out.dtype
     if T == 0:
         return out
     if x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16:
-        a = x.as_strided((H, T, K), (K, x.stride(0), 1))
-        o = out.as_strided((H, T, N), (N, H * N, 1))
+        a = x.as_strided((H, T, K), (xs, x.stride(0), 1), x.storage_offset())
+        o = out.as_strided((H, T, N), (os_, out.stride(0), 1), out.storage_offset())
         if out_dtype == torch.bfloat16:
-            torch.bmm(a, w.transpose(1, 2), out=o)
+            if os_ == N:
+                torch.bmm(a, w.transpose(1, 2), out=o)
+            else:
+                o.copy_(torch.bmm(a, w.transpose(1, 2)))
         else:
             o.copy_(torch.bmm(a, w.transpose(1, 2), out_dtype=out_dtype))
         return out
     for h in range(H):
-        call("common", "fmx_gemm_simple", x.data_ptr() + h * K * x.element_size(), w[h].data_ptr(), None,
-             out.data_ptr() + h * N * out.element_size(), T, N, K, x.stride(0), K, H * N, _dt(x), _dt(w), _dt(out), _stream())
+        call("common", "fmx_gemm_simple", x.data_ptr() + h * xs * x.element_size(), w[h].data_ptr(), None,
+             out.data_ptr() + h * os_ * out.element_size(), T, N, K, x.stride(0), K, out.stride(0), _dt(x), _dt(w), _dt(out),
+             _stream())
     return out
 
 

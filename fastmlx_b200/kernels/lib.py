@@ -49,6 +49,16 @@ _SIGNATURES = {
         "fmx_sigmoid_gate": [_P, _L, _I, _P, _L, _I, _I, _I, _I, _P],
         "fmx_moe_route": [_P, _L, _I, _I, _I, _I, _I, _P, _P, _P],
         "fmx_moe_expert_act": [_P, _L, _P, _P, _L, _I, _I, _I, _I, _F, _F, _I, _I, _P],
+        "fmx_embed_bigram": [_P, _P, _P, _P, _P, _P, _P, _P, _L, _P, _I, _I, _L, _L, _L, _L, _I, _I, _I, _P, _P],
+        "fmx_paged_attention_masked_ex": [_P, _L, _I, _P, _P, _I, _P, _P, _P, _L, _I, _I, _I, _I, _I, _I, _L, _F, _F, _I, _I,
+                                          _I, _P, _I, _I, _P, _L, _I, _P, _I, _P],
+        "fmx_qk_prepare_whole": [_P, _L, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _F, _I, _L, _I, _I, _P, _P, _P, _I,
+                                 _P, _P],
+        "fmx_latent_rope_prepare": [_P, _L, _I, _P, _L, _P, _P, _P, _F, _P, _P, _L, _I, _P, _I, _I, _I, _I, _I, _P, _P],
+        "fmx_ssm_prepare": [_P, _L, _P, _P, _P, _P, _P, _P, _P, _P, _L, _L, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _I, _P, _P],
+        "fmx_ssm_scan": [_P, _P, _P, _P, _P, _P, _L, _P, _I, _I, _I, _I, _I, _I, _I, _P],
+        "fmx_gated_group_rmsnorm": [_P, _P, _L, _P, _P, _L, _I, _I, _I, _F, _I, _P],
+        "fmx_act_mul": [_P, _P, _I, _I, _I, _I, _I, _P],
     },
     "bf16": {
         "fmx_gemv": [_P, _L, _P, _L, _P, _P, _L, _P, _L, _I, _I, _I, _I, _I, _I, _I, _P],

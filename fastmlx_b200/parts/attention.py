@@ -153,7 +153,7 @@ class GQAAttention(Mixer):
         if self.chunk or self.sinks is not None or self.gate_per_head:
             # runs of positions, a term without a value in the denominator, one gate value per head
             opts = dict(chunk=self.chunk, sinks=self.sinks, gate=gate, gate_group=self.vd if self.gate_per_head else 1)
-            wide_ex = getattr(k, "wide_attention_takes", None)
+            wide_ex = getattr(k, "wide_attention_takes", None) if getattr(k, "WIDE_HAS_SINKS", False) else None
             if wide_ex is not None and wide_ex(q, cache.kv, self.hd, self.vd, out):
                 return k.paged_attention_wide(q, cache.kv, ctx, g, self.nh, self.nkv, self.hd, self.scale, self.softcap,
                                               self.window, out=out, keep_first=self.keep_first, **opts)

@@ -126,7 +126,7 @@ class LatentAttention(Mixer):
                               ctx.status)
         k.head_linear(q, self.uk_t, torch.float32, x_head_stride=self.hd + R, out=q_lat, out_head_stride=self.row)
         opts = dict(sinks=self.sinks) if self.sinks is not None else {}
-        wide = getattr(k, "wide_attention_takes", None)
+        wide = getattr(k, "wide_attention_takes", None) if (not opts or getattr(k, "WIDE_HAS_SINKS", False)) else None
         if wide is not None and wide(q_lat, cache.kv, self.row, self.row, None):
             o_lat = k.paged_attention_wide(q_lat, cache.kv, ctx, g, self.nh, 1, self.row, self.scale, 0.0, self.window, **opts)
         else:
