@@ -495,7 +495,8 @@ attn_prefill_kernel(const void* __restrict__ q_any, long long q_stride, const bf
                     const int* __restrict__ block_tables, int bt_stride, const int* __restrict__ row_start,
                     const int* __restrict__ row_ctx, bf16* __restrict__ out, int nh, int nkv, int page_size,
                     long long num_pages, float scale, int window, int* status, float softcap, long long out_stride,
-                    const int* __restrict__ positions, float* split_out, int n_splits, int keep_first, int keys_only) {
+                    const int* __restrict__ positions, float* split_out, int n_splits, int keep_first, int keys_only,
+                    int chunk, const float* __restrict__ sinks) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   bf16* smem = reinterpret_cast<bf16*>(smem_raw);
   // The last query tiles of a row see the most keys.  Blocks start in the order x, y, z: with the
@@ -520,6 +521,9 @@ attn_prefill_kernel(const void* __restrict__ q_any, long long q_stride, const bf
   const Cache c{kv, block_tables + (long long)r * bt_stride, bt_stride, nkv, page_size, num_pages,
                 page_shift_of(page_size), WIDE ? keys_only : 0};
   const int keep = WIDE && window > 0 ? keep_first : 0;      // a request's first tokens that stay visible behind the window
+  // the first key a query at position p sees: its window's start, or (WIDE) the start of the run of `chunk` positions
+  // it lies in, runs counted from position 0
+  auto lo_of = [&](int p) { return window > 0 ? max(0, p - window + 1) : (WIDE && chunk > 0 && p > 0 ? p - p % chunk : 0); };
 
   // the two packed rows of this thread
   int prow[2], tok[2], head[2], lim[2], lo[2];
@@ -532,7 +536,7 @@ attn_prefill_kernel(const void* __restrict__ q_any, long long q_stride, const bf
     tok[x] = pr / rep;
     head[x] = g * rep + pr - tok[x] * rep;
     lim[x] = rvalid[x] ? ctx + tok[x] : -1;
-    lo[x] = window > 0 ? max(0, ctx + tok[x] - window + 1) : 0;
+    lo[x] = lo_of(ctx + tok[x]);
   }
   // query fragments, straight from global memory
   unsigned qf[KSTEPS][4];
@@ -561,7 +565,7 @@ attn_prefill_kernel(const void* __restrict__ q_any, long long q_stride, const bf
   // keys this block needs: from the first row's window start to the last row's position
   const int first_tok = prow0 / rep;
   const int last_tok = (min(prow0 + BM, n_packed) - 1) / rep;
-  int kbeg = window > 0 ? max(0, ctx + first_tok - window + 1) : 0;
+  int kbeg = lo_of(ctx + first_tok);
   if ((kbeg & ~3) < keep) kbeg = 0;                   // the window's tiles would reach into the kept tokens: one run from 0
   const int kend = ctx + last_tok + 1;
   const int kstart = kbeg & ~3;                       // tiles start on a multiple of 4 keys
@@ -577,7 +581,7 @@ attn_prefill_kernel(const void* __restrict__ q_any, long long q_stride, const bf
   // the first row's position; tiles inside that span need no mask
   const int wfirst = min(prow0 + wrow, n_packed - 1) / rep, wlast = min(prow0 + wrow + 15, n_packed - 1) / rep;
   const bool warp_full = prow0 + wrow + 15 < n_packed;
-  const int sure_lo = window > 0 ? max(0, ctx + wlast - window + 1) : 0;
+  const int sure_lo = lo_of(ctx + wlast);
   const int sure_hi = ctx + wfirst;
 
   float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
@@ -696,6 +700,13 @@ attn_prefill_kernel(const void* __restrict__ q_any, long long q_stride, const bf
         }
       }
       const int hq = g * rep + row;
+      if (WIDE && sinks != nullptr && !shared_keys) {      // the term without a value (shares leave it to the combining kernel)
+        const float sk2 = sinks[hq] * LOG2E;
+        const float M2 = fmaxf(M, sk2);
+        const float a = M == -INFINITY ? 0.f : fast_exp2(M - M2);
+        L = fmaf(L, a, fast_exp2(sk2 - M2));
+        O *= a;
+      }
       if (shared_keys) {
         float* part = split_out + (((long long)t0 * nh + hq) * n_splits + split) * (HD + 2);
         part[e] = O;
@@ -719,6 +730,14 @@ attn_prefill_kernel(const void* __restrict__ q_any, long long q_stride, const bf
       if (tq == 0) *reinterpret_cast<float2*>(part + HD) = make_float2(m[x], l[x]);
       continue;
     }
+    if (WIDE && sinks != nullptr) {                        // the term without a value
+      const float sk2 = sinks[head[x]] * LOG2E;
+      const float m2 = fmaxf(m[x], sk2);
+      const float a = m[x] == -INFINITY ? 0.f : fast_exp2(m[x] - m2);
+      l[x] = fmaf(l[x], a, fast_exp2(sk2 - m2));
+#pragma unroll
+      for (int n = 0; n < NT_O; ++n) { o[n][2 * x] *= a; o[n][2 * x + 1] *= a; }
+    }
     const float inv = l[x] > 0.f ? 1.0f / l[x] : 0.f;
     bf16* op = out + (long long)(t0 + tok[x]) * out_stride + (long long)head[x] * HD + 2 * tq;
 #pragma unroll
@@ -730,7 +749,8 @@ attn_prefill_kernel(const void* __restrict__ q_any, long long q_stride, const bf
 // The shares of a row's keys put together, one warp per (token, head), in share order: out = sum_s o_s 2^(m_s - M) /
 // sum_s l_s 2^(m_s - M) with M the largest of the shares' maxima; a row that saw no key gets zeros.
 __global__ void __launch_bounds__(128)
-attn_wide_combine_kernel(const float* part, bf16* out, long long out_stride, long long n_items, int nh, int n_splits) {
+attn_wide_combine_kernel(const float* part, bf16* out, long long out_stride, long long n_items, int nh, int n_splits,
+                         const float* __restrict__ sinks) {
   const long long item = (long long)blockIdx.x * 4 + (threadIdx.x >> 5);
   const int lane = threadIdx.x & 31;
   if (item >= n_items) return;
@@ -740,6 +760,13 @@ attn_wide_combine_kernel(const float* part, bf16* out, long long out_stride, lon
   float M = -INFINITY;
   for (int s = 0; s < n_splits; ++s) M = fmaxf(M, p[s * (HD + 2) + HD]);
   float L = 0.f;
+  if (sinks != nullptr) {                                  // one more term in the denominator, with no value
+    const float sk2 = sinks[h] * LOG2E;
+    const bool none = M == -INFINITY;
+    M = fmaxf(M, sk2);
+    L = fast_exp2(sk2 - M);
+    if (none) M = -INFINITY;                               // a row that saw no key: zeros
+  }
   float acc[(HD + 31) / 32];
 #pragma unroll
   for (int i = 0; i < (HD + 31) / 32; ++i) acc[i] = 0.f;
@@ -1276,7 +1303,7 @@ FMX_EXPORT int fmx_attn_prefill(const void* q, long long q_stride, const void* k
   dim3 grid(nkv, rows, (unsigned)tiles);
   attn_prefill_kernel<false><<<grid, THREADS, prefill_smem(), stream>>>(
       q, q_stride, (const bf16*)kv, block_tables, bt_stride, row_start, row_ctx, (bf16*)out, nh, nkv,
-      page_size, num_pages, scale, window, status, 0.f, (long long)nh * HD, (const int*)nullptr, (float*)nullptr, 1, 0, 0);
+      page_size, num_pages, scale, window, status, 0.f, (long long)nh * HD, (const int*)nullptr, (float*)nullptr, 1, 0, 0, 0, (const float*)nullptr);
   FMX_LAUNCH_CHECK();
   return 0;
 }
@@ -1286,13 +1313,17 @@ FMX_EXPORT int fmx_attn_prefill(const void* q, long long q_stride, const void* k
 // positions (or null): the step's token positions; a row whose first token stands at -1 is padding and gets zeros.
 // keep_first: beside a window, a request's first tokens that stay visible; keys_only: pages of keys [nkv, page, HD]
 // that are the values too.
-FMX_EXPORT int fmx_attn_prefill_wide_ex(const float* q, long long q_stride, const void* kv, const int* block_tables,
-                                        int bt_stride, const int* row_start, const int* row_ctx, const int* positions, void* out,
-                                        long long out_stride, int rows, int max_q_len, int nh, int nkv, int page_size,
-                                        long long num_pages, float scale, float softcap, int window, int* status,
-                                        float* scratch, long long scratch_floats, int n_splits, int n_tokens, int keep_first,
-                                        int keys_only, cudaStream_t stream) {
+// chunk (instead of a window): keys are seen within runs of this many positions, counted from position 0; sinks (or
+// null): one number per query head whose exponential is one more term of the denominator, with no value.
+FMX_EXPORT int fmx_attn_prefill_wide_masked(const float* q, long long q_stride, const void* kv, const int* block_tables,
+                                            int bt_stride, const int* row_start, const int* row_ctx, const int* positions,
+                                            void* out, long long out_stride, int rows, int max_q_len, int nh, int nkv,
+                                            int page_size, long long num_pages, float scale, float softcap, int window,
+                                            int* status, float* scratch, long long scratch_floats, int n_splits, int n_tokens,
+                                            int keep_first, int keys_only, int chunk, const float* sinks,
+                                            cudaStream_t stream) {
   if (rows == 0 || max_q_len == 0) return 0;
+  if (chunk < 0 || (chunk > 0 && window > 0)) return fmx_fail("fmx_attn_prefill_wide: chunk=%d beside window=%d", chunk, window);
   if (keep_first < 0) return fmx_fail("fmx_attn_prefill_wide: keep_first=%d", keep_first);
   if (rows < 0 || nh <= 0 || nkv <= 0 || nh % nkv || page_size <= 0)
     return fmx_fail("fmx_attn_prefill_wide: bad sizes rows=%d nh=%d nkv=%d page=%d", rows, nh, nkv, page_size);
@@ -1319,16 +1350,27 @@ FMX_EXPORT int fmx_attn_prefill_wide_ex(const float* q, long long q_stride, cons
     dim3 grid(nkv, rows, (unsigned)n_splits);
     attn_prefill_kernel<true><<<grid, THREADS, prefill_smem(), stream>>>(
         q, q_stride, (const bf16*)kv, block_tables, bt_stride, row_start, row_ctx, (bf16*)out, nh, nkv, page_size,
-        num_pages, scale, window, status, softcap, out_stride, positions, scratch, n_splits, keep_first, keys_only);
+        num_pages, scale, window, status, softcap, out_stride, positions, scratch, n_splits, keep_first, keys_only, chunk, sinks);
     FMX_LAUNCH_CHECK();
     return 0;
   }
   dim3 grid(nkv, rows, (unsigned)tiles);
   attn_prefill_kernel<true><<<grid, THREADS, prefill_smem(), stream>>>(
       q, q_stride, (const bf16*)kv, block_tables, bt_stride, row_start, row_ctx, (bf16*)out, nh, nkv, page_size,
-      num_pages, scale, window, status, softcap, out_stride, positions, (float*)nullptr, 1, keep_first, keys_only);
+      num_pages, scale, window, status, softcap, out_stride, positions, (float*)nullptr, 1, keep_first, keys_only, chunk, sinks);
   FMX_LAUNCH_CHECK();
   return 0;
+}
+
+FMX_EXPORT int fmx_attn_prefill_wide_ex(const float* q, long long q_stride, const void* kv, const int* block_tables,
+                                        int bt_stride, const int* row_start, const int* row_ctx, const int* positions, void* out,
+                                        long long out_stride, int rows, int max_q_len, int nh, int nkv, int page_size,
+                                        long long num_pages, float scale, float softcap, int window, int* status,
+                                        float* scratch, long long scratch_floats, int n_splits, int n_tokens, int keep_first,
+                                        int keys_only, cudaStream_t stream) {
+  return fmx_attn_prefill_wide_masked(q, q_stride, kv, block_tables, bt_stride, row_start, row_ctx, positions, out, out_stride,
+                                      rows, max_q_len, nh, nkv, page_size, num_pages, scale, softcap, window, status, scratch,
+                                      scratch_floats, n_splits, n_tokens, keep_first, keys_only, 0, nullptr, stream);
 }
 
 FMX_EXPORT int fmx_attn_prefill_wide(const float* q, long long q_stride, const void* kv, const int* block_tables,
@@ -1343,15 +1385,20 @@ FMX_EXPORT int fmx_attn_prefill_wide(const float* q, long long q_stride, const v
 }
 
 // Second half of a launch with n_splits > 1: tokens [first_token, first_token + n_tokens) of the step.
-FMX_EXPORT int fmx_attn_wide_combine(const float* scratch, void* out, long long out_stride, int first_token, int n_tokens,
-                                     int nh, int n_splits, cudaStream_t stream) {
+FMX_EXPORT int fmx_attn_wide_combine_sinks(const float* scratch, void* out, long long out_stride, int first_token,
+                                           int n_tokens, int nh, int n_splits, const float* sinks, cudaStream_t stream) {
   if (n_tokens <= 0) return 0;
   const long long items = (long long)n_tokens * nh;
   attn_wide_combine_kernel<<<(unsigned)((items + 3) / 4), 128, 0, stream>>>(
       scratch + (long long)first_token * nh * n_splits * (HD + 2), (bf16*)out + (long long)first_token * out_stride, out_stride,
-      items, nh, n_splits);
+      items, nh, n_splits, sinks);
   FMX_LAUNCH_CHECK();
   return 0;
+}
+
+FMX_EXPORT int fmx_attn_wide_combine(const float* scratch, void* out, long long out_stride, int first_token, int n_tokens,
+                                     int nh, int n_splits, cudaStream_t stream) {
+  return fmx_attn_wide_combine_sinks(scratch, out, out_stride, first_token, n_tokens, nh, n_splits, nullptr, stream);
 }
 
 // tickets: rows * nkv ints, zero before the first call (every call leaves them zero); with

@@ -414,6 +414,7 @@ def wide_attention_ok(q, kv, hd, vd) -> bool:
 
 
 WIDE_MAX_SPLITS = 16
+WIDE_HAS_SINKS = True            # the tiled kernel takes runs of positions and terms without a value too
 
 
 def wide_attention_splits(rows: int, nkv: int, keys: int, device=None) -> int:
@@ -433,53 +434,58 @@ def wide_attention_takes(q, kv, hd, vd, out=None) -> bool:
 
 
 def _wide_launch(q, kv, ctx, group, nh, nkv, hd, scale, softcap, window, out, first_token: int = 0, splits: int = 1,
-                 keep_first: int = 0) -> None:
+                 keep_first: int = 0, chunk: int = 0, sinks=None) -> None:
     bt = group.block_tables
     scratch = None
     n_tokens = ctx.R
     if splits > 1:
         scratch = attention_scratch(q.device, (first_token + n_tokens) * nh * splits * (hd + 2))
-    call(f"attn_hd{hd}", "fmx_attn_prefill_wide_ex", q.data_ptr(), q.stride(0), kv.data_ptr(), bt.data_ptr(), bt.stride(0),
+    call(f"attn_hd{hd}", "fmx_attn_prefill_wide_masked", q.data_ptr(), q.stride(0), kv.data_ptr(), bt.data_ptr(), bt.stride(0),
          ctx.row_start.data_ptr(), ctx.row_ctx.data_ptr(), ctx.positions.data_ptr(), out.data_ptr(), out.stride(0), ctx.R,
          int(ctx.max_q_len), nh, nkv, kv.shape[3], kv.shape[0], float(scale), float(softcap or 0.0), int(window),
          _ptr(ctx.status), _ptr(scratch), scratch.numel() if scratch is not None else 0, int(splits),
-         first_token + n_tokens, int(keep_first), int(kv.shape[1] == 1), _stream())
+         first_token + n_tokens, int(keep_first), int(kv.shape[1] == 1), int(chunk), _ptr(sinks), _stream())
     if splits > 1:
-        call(f"attn_hd{hd}", "fmx_attn_wide_combine", scratch.data_ptr(), out.data_ptr(), out.stride(0), int(first_token),
-             n_tokens, nh, int(splits), _stream())
+        call(f"attn_hd{hd}", "fmx_attn_wide_combine_sinks", scratch.data_ptr(), out.data_ptr(), out.stride(0), int(first_token),
+             n_tokens, nh, int(splits), _ptr(sinks), _stream())
 
 
 def paged_attention_wide(q, kv, ctx, group, nh, nkv, hd, scale, softcap, window, out=None, keep_first: int = 0,
-                         gate=None) -> torch.Tensor:
+                         gate=None, chunk: int = 0, sinks=None, gate_group: int = 1) -> torch.Tensor:
     """Attention of any mix of rows on the tensor cores with 32-bit scores and weights: the 32-bit queries
     q[T, nh*hd] and the probabilities enter the products as two bfloat16 terms each, sums are 32-bit, scores may be
     capped (softcap > 0).  `out` may be a slice of a wider buffer.  -> [T, nh*hd] in bfloat16.  The one-token rows
     (a whole decode step, or the rows at the head of a mixed step) have their keys shared out over several blocks
     whose parts a second kernel puts together; the portions behind them take a launch of their own.
     `keep_first`: beside a window, a request's first tokens that stay visible; pages of shape [pages, 1, nkv, page, hd]
-    hold keys that are the values too; `gate` ([T, nh*hd]): the output is multiplied by sigmoid(gate) afterwards."""
-    out = _paged_attention_wide(q, kv, ctx, group, nh, nkv, hd, scale, softcap, window, out, int(keep_first))
+    hold keys that are the values too; `gate` ([T, nh*hd / gate_group]): the output is multiplied by sigmoid(gate)
+    afterwards, one gate value per `gate_group` elements.  `chunk` c > 0 instead of a window: keys are seen within runs
+    of c positions counted from position 0; `sinks` (32-bit [nh]): one more term exp(sink) per head in the
+    denominator, with no value."""
+    assert sinks is None or (sinks.dtype == torch.float32 and sinks.is_contiguous() and sinks.numel() == nh)
+    out = _paged_attention_wide(q, kv, ctx, group, nh, nkv, hd, scale, softcap, window, out, int(keep_first), int(chunk), sinks)
     if gate is not None:
-        sigmoid_gate(out, gate, 1)
+        sigmoid_gate(out, gate, int(gate_group))
     return out
 
 
-def _paged_attention_wide(q, kv, ctx, group, nh, nkv, hd, scale, softcap, window, out, keep_first) -> torch.Tensor:
+def _paged_attention_wide(q, kv, ctx, group, nh, nkv, hd, scale, softcap, window, out, keep_first, chunk=0, sinks=None) -> torch.Tensor:
     T = q.shape[0]
     if out is None:
         out = torch.empty((T, nh * hd), dtype=torch.bfloat16, device=q.device)
     assert out.dtype == torch.bfloat16 and out.stride(1) == 1 and out.stride(0) % 2 == 0 and out.data_ptr() % 4 == 0
     d = ctx.R if ctx.all_decode else getattr(ctx, "decode_rows", 0)
+    more = dict(chunk=chunk, sinks=sinks)
     if d <= 0:
-        _wide_launch(q, kv, ctx, group, nh, nkv, hd, scale, softcap, window, out, keep_first=keep_first)
+        _wide_launch(q, kv, ctx, group, nh, nkv, hd, scale, softcap, window, out, keep_first=keep_first, **more)
         return out
     longest = ctx.max_ctx_after if ctx.all_decode else ctx.decode_max_ctx
-    keys = min(window + keep_first, longest) if window > 0 else longest
+    keys = min(window + keep_first, longest) if window > 0 else (min(chunk, longest) if chunk > 0 else longest)
     splits = wide_attention_splits(d, nkv, keys, q.device)
     if splits > 1 and d * nh * splits * (hd + 2) > ATTN_SCRATCH_FLOATS:
         splits = 1
     if ctx.all_decode:
-        _wide_launch(q, kv, ctx, group, nh, nkv, hd, scale, softcap, window, out, 0, splits, keep_first)
+        _wide_launch(q, kv, ctx, group, nh, nkv, hd, scale, softcap, window, out, 0, splits, keep_first, **more)
         return out
     key = ("wide attention rows", id(group))
     views = ctx.scratch.get(key)
@@ -487,8 +493,8 @@ def _paged_attention_wide(q, kv, ctx, group, nh, nkv, hd, scale, softcap, window
         views = ctx.scratch[key] = (_rows_of(ctx, group, 0, d, 1, ctx.decode_max_ctx),
                                     _rows_of(ctx, group, d, ctx.R, ctx.rest_max_q_len, ctx.rest_max_ctx))
     (dctx, dgroup), (rctx, rgroup) = views
-    _wide_launch(q, kv, dctx, dgroup, nh, nkv, hd, scale, softcap, window, out, 0, splits, keep_first)     # the one-token rows come first
-    _wide_launch(q, kv, rctx, rgroup, nh, nkv, hd, scale, softcap, window, out, keep_first=keep_first)
+    _wide_launch(q, kv, dctx, dgroup, nh, nkv, hd, scale, softcap, window, out, 0, splits, keep_first, **more)     # the one-token rows come first
+    _wide_launch(q, kv, rctx, rgroup, nh, nkv, hd, scale, softcap, window, out, keep_first=keep_first, **more)
     return out
 
 

@@ -82,6 +82,9 @@ _SIGNATURES = {
         "fmx_attn_prefill_wide_ex": [_P, _L, _P, _P, _I, _P, _P, _P, _P, _L, _I, _I, _I, _I, _I, _L, _F, _F, _I, _P, _P, _L, _I, _I,
                                      _I, _I, _P],
         "fmx_attn_wide_combine": [_P, _P, _L, _I, _I, _I, _I, _P],
+        "fmx_attn_prefill_wide_masked": [_P, _L, _P, _P, _I, _P, _P, _P, _P, _L, _I, _I, _I, _I, _I, _L, _F, _F, _I, _P, _P, _L, _I,
+                                         _I, _I, _I, _I, _P, _P],
+        "fmx_attn_wide_combine_sinks": [_P, _P, _L, _I, _I, _I, _I, _P, _P],
         "fmx_attn_decode": [_P, _L, _P, _P, _I, _P, _P, _P, _P, _L, _P, _I, _I, _I, _I, _I, _L, _F, _I, _P, _P, _I, _I, _I, _P],
     },
 }
