@@ -414,6 +414,32 @@ def gekavik_like(shape: dict, layers: int, window: int = 1024) -> dict:
     return cfg
 
 
+def sorupel_like(shape: dict, layers: int, chunk: int = 1024) -> dict:
+    """A Sorupel configuration with a Llama shape's width, heads and vocabulary: layers in the pattern state space,
+    chunked attention whose values are its keys, latent attention, latent attention that reads the layer before it; the
+    recurrence has twice the width in channels (heads of 64, a state of 128 rows, 8 groups), the latent 192 values and a
+    rotated part of 64, and every layer the gated feed-forward of the Llama layer with the tanh form of gelu."""
+    d, nh, nkv, hd = shape["hidden_size"], shape["num_attention_heads"], shape["num_key_value_heads"], shape["head_dim"]
+    mlp = {"kind": "dense", "ff": shape["intermediate_size"]}
+    ssm = {"type": "mamba2", "mlp": mlp,
+           "mixer": {"heads": 2 * d // 64, "vdim": 64, "state": 128, "groups": 8, "norm_groups": 8, "conv": 4}}
+    att = {"type": "attention", "mlp": mlp,
+           "mixer": {"heads": nh, "kv_heads": nkv, "dim": hd, "vdim": hd, "scale": hd ** -0.5, "softcap": 30.0,
+                     "mask": {"size": chunk}, "rot": {"dims": hd // 2, "base": 10000.0}}}
+
+    def lat(src=None):
+        m = {"heads": nh, "dim": hd, "rot_dim": 64, "vdim": hd, "kv_rank": 192, "scale": (hd + 64) ** -0.5,
+             "rot": {"dims": 64, "base": 10000.0}}
+        if src is not None:
+            m["kv_from"] = src
+        return {"type": "latent_attention", "mlp": mlp, "mixer": m}
+    out = []
+    for i in range(layers):
+        out.append(ssm if i % 4 == 0 else att if i % 4 == 1 else lat() if i % 4 == 2 else lat(i - 1))
+    return {"architecture": "Sorupel", "vocab": shape["vocab_size"], "width": d, "norm": {"eps": 1e-6},
+            "embedding": {"bigram": {"buckets": 99991, "mul_prev": 31337, "mul_cur": 7919}}, "layers": out}
+
+
 def step_weight_bytes(model, tokens: int) -> int:
     """Bytes of weights a step of `tokens` tokens must read: every run of the schedule reads its layer (a looped layer
     once per pass); a routed feed-forward with grouped products reads the experts its tokens chose, at most."""
@@ -459,12 +485,27 @@ def design_numbers(cfg: dict, vocab: int, pk: dict, context: int, steps: int, wa
     return out
 
 
+def design_steps(cfg: dict, vocab: int, batch: int, context: int, steps: int, warmup: int, graphs: bool) -> None:
+    """For a profiler's launch list of one design: a 2,048-token prompt step, then `steps` decode steps of `batch`
+    requests behind `context` tokens; no timing."""
+    import torch
+    from fastmlx_b200 import Engine
+    engine = Engine(config=cfg, weights_seed=0, dtype="bfloat16", block_size=16, max_cache_tokens=batch * (context + 64) + 4096,
+                    max_concurrent_requests=max(batch, 1), max_num_batched_tokens=8192, cuda_graphs=graphs)
+    prefill_through_engine(engine, PREFILL_TOKENS, vocab, repeats=1)
+    ids = fill(engine, batch, context - steps - warmup - 4, vocab, seed=1000 * batch)
+    for _ in range(warmup + steps):
+        engine.step()
+    drain(engine, ids)
+    torch.cuda.synchronize()
+
+
 def compare_designs(shapes, layers: int, context: int, steps: int, warmup: int, pk: dict, which=("llama", "medirax")) -> dict:
     out = {}
     for key in shapes:
         name, shape = SHAPES[key]
         make = {"llama": lambda: dict(shape, num_hidden_layers=layers), "medirax": lambda: medirax_like(shape, layers),
-                "gekavik": lambda: gekavik_like(shape, layers)}
+                "gekavik": lambda: gekavik_like(shape, layers), "sorupel": lambda: sorupel_like(shape, layers)}
         out[key] = {"layers": layers, "context": context}
         for design in which:
             out[key][design] = design_numbers(make[design](), shape["vocab_size"], pk, context, steps, warmup)
@@ -490,9 +531,10 @@ def main() -> int:
                     "layers of equal size are measured side by side; prints that comparison alone")
     ap.add_argument("--design-layers", type=int, default=8, help="layers of each model of the --designs comparison")
     ap.add_argument("--design-set", default="llama,medirax", help="which designs the --designs comparison measures "
-                    "(comma-separated, of llama, medirax, gekavik)")
+                    "(comma-separated, of llama, medirax, gekavik, sorupel)")
     ap.add_argument("--only-steps", type=int, default=0,
-                    help="for a profiler's launch list: fill the batch, run this many decode steps and stop (no timing, no JSON line)")
+                    help="for a profiler's launch list: fill the batch, run this many decode steps and stop (no timing, no JSON line); "
+                    "with --designs: a 2,048-token prompt step and the decode steps of the first design named, at the first size named")
     args = ap.parse_args()
 
     if args.impl == "reference":
@@ -515,9 +557,17 @@ def main() -> int:
     if args.designs:
         keys = [k for k in args.designs.split(",") if k]
         which = [w for w in args.design_set.split(",") if w]
-        if any(w not in ("llama", "medirax", "gekavik") for w in which):
-            print(f"bench.py: --design-set takes llama, medirax, gekavik (got {args.design_set!r})")
+        if any(w not in ("llama", "medirax", "gekavik", "sorupel") for w in which):
+            print(f"bench.py: --design-set takes llama, medirax, gekavik, sorupel (got {args.design_set!r})")
             return 2
+        if args.only_steps > 0:
+            shape = SHAPES[keys[0]][1]
+            make = {"llama": lambda: dict(shape, num_hidden_layers=args.design_layers), "medirax": lambda: medirax_like(shape, args.design_layers),
+                    "gekavik": lambda: gekavik_like(shape, args.design_layers), "sorupel": lambda: sorupel_like(shape, args.design_layers)}
+            design_steps(make[which[0]](), shape["vocab_size"], args.batch, min(args.context, 4096), args.only_steps, warmup,
+                         not args.no_cuda_graphs)
+            print(f"ran a {PREFILL_TOKENS}-token prompt step and {args.only_steps} decode steps of batch {args.batch} of {which[0]} at the {keys[0]} sizes")
+            return 0
         print(json.dumps({"compare": " beside ".join(which) + " at equal layer sizes", "dtype": "bf16",
                           "data": "synthetic: seeded uniform-random token ids, random weights", "peaks": pk["source"],
                           "designs": compare_designs(keys, args.design_layers, min(args.context, 4096), min(steps, 64), warmup, pk,

@@ -47,11 +47,16 @@ __device__ __forceinline__ unsigned long long greedy_key(float v, int n) {
   return ((unsigned long long)u << 32) | (unsigned)(0x7fffffff - n);
 }
 
+constexpr int GATE_SHIFT = 20;
+
 template <int NT, bool HI, bool DUAL, int U, int WARPS, typename TO, bool GREEDY = false>
 __global__ void __launch_bounds__(WARPS * 32)
 gemv_kernel(const bf16* x, long long ldx, const bf16* __restrict__ W, long long ldw, const float* __restrict__ bias,
-            const bf16* residual, long long ldr, TO* out, long long ldo, int M, int N, int K, int blk,
+            const bf16* residual, long long ldr, TO* out, long long ldo, int M, int N, int K, int blk_in,
             GreedyOut greedy = GreedyOut{nullptr, nullptr, nullptr, 0}) {
+  // a gated product's block size carries the gate's activation above GATE_SHIFT (0: silu, 1: the tanh form of gelu)
+  const int gate_kind = DUAL ? (blk_in >> GATE_SHIFT) : 0;
+  const int blk = DUAL ? (blk_in & ((1 << GATE_SHIFT) - 1)) : blk_in;
   constexpr int TILES = DUAL ? 2 * NT : NT;
   constexpr int ROWS = HI ? 16 : 8;
   __shared__ float red[WARPS][TILES][ROWS][9];
@@ -176,7 +181,9 @@ gemv_kernel(const bf16* x, long long ldx, const bf16* __restrict__ W, long long 
 #pragma unroll
       for (int w = 0; w < WARPS; ++w) up += red[w][NT + i][tok][f];
       const float gte = bf16r(v);
-      v = gte / (1.0f + expf(-gte)) * bf16r(up);
+      const float act = gate_kind == 1 ? 0.5f * gte * (1.0f + tanhf(0.7978845608028654f * (gte + 0.044715f * gte * gte * gte)))
+                                       : gte / (1.0f + expf(-gte));
+      v = act * bf16r(up);
     }
     if (bias != nullptr) v += bias[n];
     if (!DUAL && blk < 0) {                         // as the unfused path rounds: the product first, then its activation
@@ -268,7 +275,7 @@ FMX_EXPORT int fmx_gemv_plan_warps(int n_out, int K, int wide, int sms) {
 // x [M <= 16, K] and W [N, K] bfloat16, rows 16-byte aligned; out [M, N] bfloat16 (out_dtype 1)
 // or float (0); bias float[N] or null; residual bfloat16 [M, n_out] or null (may be `out`).
 // blk > 0: W's rows alternate in blocks of blk gate rows and blk up rows, out is [M, N/2] =
-// silu(gate) * up in bfloat16.  blk < 0: out = act(product + bias) in bfloat16, act = relu^2 (-1), gelu-tanh (-2), silu (-3).  wide: 8, 16 or 32 output features per block; warps: 8 or 16
+// silu(gate) * up in bfloat16 (blk + (1 << 20): the tanh form of gelu instead of silu).  blk < 0: out = act(product + bias) in bfloat16, act = relu^2 (-1), gelu-tanh (-2), silu (-3).  wide: 8, 16 or 32 output features per block; warps: 8 or 16
 // per block (16 when few blocks must keep many bytes in flight over a long K).
 FMX_EXPORT int fmx_gemv(const void* x, long long ldx, const void* W, long long ldw, const float* bias, const void* residual,
                         long long ldr, void* out, long long ldo, int M, int N, int K, int out_dtype, int blk, int wide,
@@ -277,7 +284,10 @@ FMX_EXPORT int fmx_gemv(const void* x, long long ldx, const void* W, long long l
   if (M < 0 || M > 16 || N < 0 || K <= 0) return fmx_fail("fmx_gemv: takes 1..16 rows, got M=%d N=%d K=%d", M, N, K);
   if (K % 8 || ldx % 8 || ldw % 8 || ((uintptr_t)x & 15) || ((uintptr_t)W & 15))
     return fmx_fail("fmx_gemv: rows must be 16-byte aligned (K=%d ldx=%lld ldw=%lld)", K, ldx, ldw);
-  if (blk < -3 || (blk > 0 && (blk % 16 || N % (2 * blk))))
+  const int gate_flag = blk > 0 ? (blk >> GATE_SHIFT) << GATE_SHIFT : 0;
+  if (blk > 0) blk -= gate_flag;
+  if (gate_flag >> GATE_SHIFT > 1) return fmx_fail("fmx_gemv: the gate's activation is silu (0) or gelu (1), not %d", gate_flag >> GATE_SHIFT);
+  if (blk < -3 || blk == 0 && gate_flag || (blk > 0 && (blk % 16 || N % (2 * blk))))
     return fmx_fail("fmx_gemv: gate/up blocks of %d do not tile %d rows", blk, N);
   if (blk < 0 && out_dtype != FMX_BF16) return fmx_fail("fmx_gemv: an activation epilogue writes bfloat16");
   if (blk > 0 && out_dtype != FMX_BF16) return fmx_fail("fmx_gemv: the SiLU-mul epilogue writes bfloat16");
@@ -290,7 +300,7 @@ FMX_EXPORT int fmx_gemv(const void* x, long long ldx, const void* W, long long l
   if (wide != 8 && wide != 16 && wide != 32) return fmx_fail("fmx_gemv: 8, 16 or 32 features per block, not %d", wide);
   if (blk > 0 && blk % wide) return fmx_fail("fmx_gemv: %d features per block do not tile gate/up blocks of %d", wide, blk);
 #define FMX_GV1(NT_, HI_, DUAL_, U_, W_, TO_) \
-  launch<NT_, HI_, DUAL_, U_, W_, TO_>(x, ldx, W, ldw, bias, residual, ldr, out, ldo, M, N, K, blk, stream)
+  launch<NT_, HI_, DUAL_, U_, W_, TO_>(x, ldx, W, ldw, bias, residual, ldr, out, ldo, M, N, K, blk | gate_flag, stream)
 #define FMX_GV(NT_, HI_, DUAL_, U_, TO_)                 \
   do {                                                   \
     if (warps == 16) FMX_GV1(NT_, HI_, DUAL_, U_, 16, TO_); \

@@ -25,32 +25,40 @@
 #include "conv_state.cuh"
 
 namespace {
+constexpr int PREP_CHANNELS = 512;               // channels of a token that one block of ssm_prepare takes
 // proj [T, stride]: z (H*P) | x (H*P) | B (G*N) | C (G*N) | dt (H).  out_xbc [T, C] 32-bit; out_dd [T, 2H]: dt | decay.
 template <typename T>
 __global__ void __launch_bounds__(128)
-ssm_prepare_kernel(const T* proj, long long stride, const float* __restrict__ conv_w, const float* __restrict__ conv_b,
-                   const float* __restrict__ a_log, const float* __restrict__ dt_bias, const int* token_row,
-                   const int* row_start, const int* row_slot, const float* state, long long slot_stride, long long conv_off,
-                   float* out_xbc, float* out_dd, int H, int C, int inner, int taps, int R, int max_slots, int* status) {
+ssm_prepare_kernel(const T* __restrict__ proj, long long stride, const float* __restrict__ conv_w,
+                   const float* __restrict__ conv_b, const float* __restrict__ a_log, const float* __restrict__ dt_bias,
+                   const int* __restrict__ token_row, const int* __restrict__ row_start, const int* __restrict__ row_slot,
+                   const float* __restrict__ state, long long slot_stride, long long conv_off, float* __restrict__ out_xbc,
+                   float* __restrict__ out_dd, int H, int C, int inner, int taps, int R, int max_slots, int* status) {
   pdl_wait();
   pdl_trigger();
+  // grid (T, ceil(C / PREP_CHANNELS)): a block takes a run of a token's channels, so that a step of few tokens still
+  // fills the GPU; the blocks of the first run also take the token's step sizes and decays
   const int t = blockIdx.x;
+  const int c_lo = blockIdx.y * PREP_CHANNELS, c_hi = min(C, c_lo + PREP_CHANNELS);
   const int r = token_row[t];
   float* ox = out_xbc + (long long)t * C;
   float* od = out_dd + (long long)t * 2 * H;
   const int slot = (r >= 0 && r < R) ? row_slot[r] : -1;
   if (slot < 0 || slot >= max_slots) {          // a padding row of a captured step, or a bad row: nothing to do
-    if (r < 0 || r >= R) { if (threadIdx.x == 0) fmx_set_status(status, FMX_BAD_ROW, r, t); }
-    else if (slot >= max_slots && threadIdx.x == 0) fmx_set_status(status, FMX_BAD_SLOT, slot, t);
-    for (int c = threadIdx.x; c < C; c += blockDim.x) ox[c] = 0.f;
-    for (int c = threadIdx.x; c < 2 * H; c += blockDim.x) od[c] = 0.f;
+    if (blockIdx.y == 0) {
+      if (r < 0 || r >= R) { if (threadIdx.x == 0) fmx_set_status(status, FMX_BAD_ROW, r, t); }
+      else if (slot >= max_slots && threadIdx.x == 0) fmx_set_status(status, FMX_BAD_SLOT, slot, t);
+      for (int c = threadIdx.x; c < 2 * H; c += blockDim.x) od[c] = 0.f;
+    }
+    for (int c = c_lo + threadIdx.x; c < c_hi; c += blockDim.x) ox[c] = 0.f;
     return;
   }
   const int first = row_start[r];
   const int i = t - first;                       // the token's place in its portion
   const float* cstate = state + (long long)slot * slot_stride + conv_off;     // [taps-1, C]
   const T* in = proj + inner;                    // the convolution's channels start behind z
-  for (int c = threadIdx.x; c < C; c += blockDim.x) {
+#pragma unroll 4
+  for (int c = c_lo + threadIdx.x; c < c_hi; c += blockDim.x) {
     float acc = conv_b[c];
     for (int j = 0; j < taps; ++j) {
       const int n = i - (taps - 1) + j;
@@ -59,6 +67,7 @@ ssm_prepare_kernel(const T* proj, long long stride, const float* __restrict__ co
     }
     ox[c] = silu_f(acc);
   }
+  if (blockIdx.y != 0) return;
   for (int h = threadIdx.x; h < H; h += blockDim.x) {
     const float a = to_f(proj[(long long)t * stride + inner + C + h]) + dt_bias[h];
     const float dt = a > 20.f ? a : log1pf(expf(a));
@@ -234,7 +243,7 @@ FMX_EXPORT int fmx_ssm_prepare(const void* proj, long long stride, const float* 
   if (stride < 2 * inner + 2 * G * N + H) return fmx_fail("fmx_ssm_prepare: rows too narrow");
 #define FMX_SSM_PREP(TT)                                                                                               \
   do {                                                                                                                 \
-    fmx_launch(ssm_prepare_kernel<TT>, dim3(T), dim3(128), 0, stream, (const TT*)proj, stride, conv_w, conv_b, a_log,  \
+    fmx_launch(ssm_prepare_kernel<TT>, dim3(T, (C + PREP_CHANNELS - 1) / PREP_CHANNELS), dim3(128), 0, stream, (const TT*)proj, stride, conv_w, conv_b, a_log,  \
                dt_bias, token_row, row_start, row_slot, (const float*)state, slot_stride, conv_off, out_xbc, out_dd, H, C, \
                inner, taps, R, max_slots, status);                                                                     \
     fmx_launch(conv_state_update_kernel<TT>, dim3((C + 127) / 128, R), dim3(128), 0, stream, (const TT*)proj + inner,  \

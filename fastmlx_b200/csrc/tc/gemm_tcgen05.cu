@@ -37,7 +37,8 @@ constexpr int THREADS = 192;
 
 // RELU2: max(x, 0)^2.  EXPERT: a routed expert's gated activation, w g' sigmoid(1.702 g') (u' + 1) with g' = min(g, limit),
 // u' = clamp(u, -limit, limit) and w the row's weight, over gate/up blocks like SILU_MUL.  F32: the product as 32-bit floats.
-enum Epilogue { EPI_PLAIN = 0, EPI_SILU_MUL = 1, EPI_RESIDUAL = 2, EPI_RELU2 = 3, EPI_EXPERT = 4, EPI_F32 = 5 };
+// GELU_MUL: SILU_MUL with the tanh form of gelu on the gate.
+enum Epilogue { EPI_PLAIN = 0, EPI_SILU_MUL = 1, EPI_RESIDUAL = 2, EPI_RELU2 = 3, EPI_EXPERT = 4, EPI_F32 = 5, EPI_GELU_MUL = 6 };
 
 // A grouped product: the rows of A are (token, expert) pairs sorted expert by expert, each expert's rows starting on a
 // multiple of 128, and tile row m multiplies with the matrix of expert tile_expert[m], which lies expert_rows rows further
@@ -66,6 +67,9 @@ __device__ __forceinline__ unsigned pack2(float lo, float hi) {
   return *reinterpret_cast<unsigned*>(&v);
 }
 __device__ __forceinline__ float silu(float g) { return g / (1.0f + expf(-g)); }
+__device__ __forceinline__ float gelu_tanh(float g) {
+  return 0.5f * g * (1.0f + tanhf(0.7978845608028654f * (g + 0.044715f * g * g * g)));
+}
 
 template <int BN, int EPI>
 __global__ void __launch_bounds__(THREADS, 1)
@@ -202,7 +206,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     int acc = 0;
     uint32_t acc_phase = 0;
     bool ok = true;
-    constexpr bool GATED = EPI == EPI_SILU_MUL || EPI == EPI_EXPERT;
+    constexpr bool GATED = EPI == EPI_SILU_MUL || EPI == EPI_GELU_MUL || EPI == EPI_EXPERT;
     constexpr int OUT_COLS = GATED ? BN / 2 : BN;
     for (int t = blockIdx.x; t < n_tiles && ok; t += gridDim.x) {
       const int m0 = (t % tiles_m) * BM, n_tile = t / tiles_m;
@@ -225,11 +229,11 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
 #pragma unroll
           for (int i = 0; i < 16; ++i) {
             f[i] = __uint_as_float(v[i]);
-            if (EPI == EPI_SILU_MUL) {
+            if (EPI == EPI_SILU_MUL || EPI == EPI_GELU_MUL) {
               // as the unfused path rounds: gate and up to bfloat16 first, then the product
               const float g = __bfloat162float(__float2bfloat16_rn(f[i]));
               const float w = __bfloat162float(__float2bfloat16_rn(__uint_as_float(u[i])));
-              f[i] = silu(g) * w;
+              f[i] = (EPI == EPI_SILU_MUL ? silu(g) : gelu_tanh(g)) * w;
             }
             if (EPI == EPI_EXPERT) {
               const float g = fminf(f[i], gr.limit);
@@ -390,8 +394,9 @@ FMX_EXPORT int fmx_gemm_tcgen05(const void* A, long long lda, const void* W, lon
   if (M < 0 || N < 0 || K <= 0) return fmx_fail("fmx_gemm_tcgen05: bad sizes M=%d N=%d K=%d", M, N, K);
   if (K % 8 || lda % 8 || ldw % 8 || ((uintptr_t)A & 15) || ((uintptr_t)W & 15))
     return fmx_fail("fmx_gemm_tcgen05: rows must start on 16-byte boundaries (K=%d lda=%lld ldw=%lld)", K, lda, ldw);
-  if (bn == 0) bn = epilogue == EPI_SILU_MUL ? 256 : fmx_gemm_tcgen05_plan_width(M, N, sms);
-  if (epilogue == EPI_SILU_MUL && N % bn) return fmx_fail("fmx_gemm_tcgen05: gate/up blocks need N a multiple of %d", bn);
+  const bool gated = epilogue == EPI_SILU_MUL || epilogue == EPI_GELU_MUL;
+  if (bn == 0) bn = gated ? 256 : fmx_gemm_tcgen05_plan_width(M, N, sms);
+  if (gated && N % bn) return fmx_fail("fmx_gemm_tcgen05: gate/up blocks need N a multiple of %d", bn);
   if (epilogue == EPI_RESIDUAL && residual == nullptr) return fmx_fail("fmx_gemm_tcgen05: the residual epilogue needs a residual");
   if (sms <= 0) sms = fmx_num_sms();
 #define FMX_TC_CASE(BN_, EPI_) \
@@ -401,6 +406,8 @@ FMX_EXPORT int fmx_gemm_tcgen05(const void* A, long long lda, const void* W, lon
   FMX_TC_CASE(128, EPI_PLAIN);
   FMX_TC_CASE(256, EPI_SILU_MUL);
   FMX_TC_CASE(128, EPI_SILU_MUL);
+  FMX_TC_CASE(256, EPI_GELU_MUL);
+  FMX_TC_CASE(128, EPI_GELU_MUL);
   FMX_TC_CASE(256, EPI_RESIDUAL);
   FMX_TC_CASE(128, EPI_RESIDUAL);
   FMX_TC_CASE(256, EPI_RELU2);

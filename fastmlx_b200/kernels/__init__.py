@@ -174,6 +174,8 @@ LIBRARY_MIN_FEATURES = 65536     # from this many output features on (the vocabu
 TC_MIN_ROWS = 128
 GATE_UP_BLOCK = 128              # gate/up rows of a fused weight alternate in blocks of this many
 EPI_PLAIN, EPI_SILU_MUL, EPI_RESIDUAL, EPI_RELU2 = 0, 1, 2, 3
+EPI_GELU_MUL = 6                 # the gated epilogue with the tanh form of gelu on the gate
+GEMV_GATE_GELU = 1 << 20         # added to a gated whole-K product's block size: gelu on the gate instead of silu
 
 
 def _bf16_operands(x, w) -> bool:
@@ -193,13 +195,17 @@ def gemv(x, w, bias=None, out_dtype=torch.bfloat16, residual=None, block: int = 
     """x[M <= 16, K] @ w[N, K]^T, one block per `wide` (8, 16, 32) output features and the whole of K:
     nothing is summed across blocks.  residual [M, n_out] is added to the product (out may be
     the residual itself).  block > 0: w's rows alternate in blocks of `block` gate rows and
-    their up rows, and the result is silu(gate) * up, [M, N/2].  act (relu2, gelu_tanh, silu): the
-    activation of the product (and bias), in the same pass; `out` may be a slice of a wider buffer."""
+    their up rows, and the result is silu(gate) * up, [M, N/2] (with act="gelu_tanh": gelu(gate) * up).  act (relu2,
+    gelu_tanh, silu) without blocks: the activation of the product (and bias), in the same pass; `out` may be a slice
+    of a wider buffer."""
     M, K = x.shape
     N = w.shape[0]
     n_out = N // 2 if block else N
-    if act is not None:
-        assert not block and out_dtype == torch.bfloat16
+    if act is not None and block:
+        assert block > 0 and act in ("silu", "gelu_tanh") and out_dtype == torch.bfloat16
+        block = int(block) + (GEMV_GATE_GELU if act == "gelu_tanh" else 0)
+    elif act is not None:
+        assert out_dtype == torch.bfloat16
         block = -1 - ACTIVATIONS[act]
     if out is None:
         out = torch.empty((M, n_out), dtype=out_dtype, device=x.device)
@@ -267,21 +273,22 @@ def can_tc(x, w, bias=None, out_dtype=torch.bfloat16, epilogue: int = EPI_PLAIN)
     that fill the GPU.  A plain product runs in the library: with the weights coming from HBM it
     is ahead of the one-CTA kernel at every size measured (2048 x 2048 x 8192: 47 us against 52)."""
     return (epilogue != EPI_PLAIN and _bf16_operands(x, w) and bias is None and out_dtype == torch.bfloat16
-            and x.shape[0] >= TC_MIN_ROWS and (epilogue != EPI_SILU_MUL or w.shape[0] % (2 * GATE_UP_BLOCK) == 0)
+            and x.shape[0] >= TC_MIN_ROWS and (epilogue not in (EPI_SILU_MUL, EPI_GELU_MUL) or w.shape[0] % (2 * GATE_UP_BLOCK) == 0)
             and tc_fills_the_gpu(x.shape[0], w.shape[0], num_sms(x.device)))
 
 
 def gemm_tcgen05(x, w, status=None, epilogue: int = EPI_PLAIN, residual=None, bn: int | None = None, out=None) -> torch.Tensor:
     """x[M, K] @ w[N, K]^T on the tcgen05 tensor cores (TMA-fed, accumulators in tensor memory).
     epilogue EPI_SILU_MUL: w's rows come in blocks of bn/2 gate rows then bn/2 up rows, and the
-    result is silu(gate) * up, [M, N/2]; EPI_RESIDUAL: residual + product; EPI_RELU2: the square of the
+    result is silu(gate) * up, [M, N/2] (EPI_GELU_MUL: the tanh form of gelu on the gate); EPI_RESIDUAL: residual + product; EPI_RELU2: the square of the
     product's positive part.  `out` may be a slice of a wider buffer."""
     M, K = x.shape
     N = w.shape[0]
     sms = num_sms(x.device)
+    n_out = N // 2 if epilogue in (EPI_SILU_MUL, EPI_GELU_MUL) else N
     if out is None:
-        out = torch.empty((M, N // 2 if epilogue == EPI_SILU_MUL else N), dtype=torch.bfloat16, device=x.device)
-    assert out.dtype == torch.bfloat16 and out.stride(1) == 1 and out.shape == (M, N // 2 if epilogue == EPI_SILU_MUL else N)
+        out = torch.empty((M, n_out), dtype=torch.bfloat16, device=x.device)
+    assert out.dtype == torch.bfloat16 and out.stride(1) == 1 and out.shape == (M, n_out)
     call("tc", "fmx_gemm_tcgen05", x.data_ptr(), x.stride(0), w.data_ptr(), w.stride(0), out.data_ptr(), out.stride(0),
          _ptr(residual), residual.stride(0) if residual is not None else 0, M, N, K, int(bn or 0), epilogue, sms,
          _ptr(status if status is not None else _status_word(x.device)), _stream())

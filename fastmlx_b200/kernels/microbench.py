@@ -6,6 +6,8 @@ launches), for tuning and for profiler captures on a small case.
     python -m fastmlx_b200.kernels.microbench --kernel gemv --M 8 --N 2048 --K 8192
     python -m fastmlx_b200.kernels.microbench --kernel gemm --M 2048 --N 16384 --K 2048
     python -m fastmlx_b200.kernels.microbench --kernel sample --batch 8 --N 128256
+    python -m fastmlx_b200.kernels.microbench --kernel recurrence --batch 1 --qlen 2048 --nh 64 --hd 64 --state 128
+    python -m fastmlx_b200.kernels.microbench --kernel attn_masked --batch 64 --qlen 1 --ctx 4096 --hd 64
 """
 from __future__ import annotations
 
@@ -56,9 +58,124 @@ def _attention_inputs(a, qlen):
     return qkv, kv, ctx, SimpleNamespace(block_tables=bt)
 
 
+def _flush():
+    """A buffer larger than L2, written between timed launches."""
+    buf = torch.empty(192 * 1024 * 1024, dtype=torch.uint8, device=DEV)
+    return lambda: buf.fill_(1)
+
+
+def _time_events(fn, reps: int, flush=None) -> float:
+    """Median microseconds of fn alone: events around each launch, L2 flushed before it."""
+    for _ in range(3):
+        fn()
+    torch.cuda.synchronize()
+    out = []
+    for _ in range(reps):
+        if flush is not None:
+            flush()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        fn()
+        e1.record()
+        torch.cuda.synchronize()
+        out.append(e0.elapsed_time(e1) * 1e3)
+    return sorted(out)[len(out) // 2]
+
+
+def _rows_ctx(B, qlen, ctx_len=0):
+    T = B * qlen
+    return SimpleNamespace(T=T, R=B, positions=torch.cat([torch.arange(ctx_len, ctx_len + qlen) for _ in range(B)]).int().to(DEV),
+                           token_row=torch.arange(B).repeat_interleave(qlen).int().to(DEV),
+                           row_start=(torch.arange(B + 1) * qlen).int().to(DEV), row_slot=torch.arange(B).int().to(DEV),
+                           row_ctx=torch.full((B,), ctx_len, dtype=torch.int32, device=DEV),
+                           status=torch.zeros(4, dtype=torch.int32, device=DEV), max_q_len=qlen, max_ctx_after=ctx_len + qlen,
+                           all_decode=qlen == 1, decode_rows=B if qlen == 1 else 0, scratch={})
+
+
+def _recurrence(a) -> int:
+    """The state-space recurrence and the gated delta rule side by side at like sizes: --nh heads of --hd values over
+    --state rows of state, --groups groups; --batch requests of --qlen tokens each.  Per kernel: microseconds (events,
+    L2 flushed) and the bytes it must move over that time."""
+    H, P, N, G, taps, B, q = a.nh, a.hd, a.state, a.groups, a.taps, a.batch, a.qlen
+    T = B * q
+    ctx = _rows_ctx(B, q)
+    flush = _flush()
+    gen = lambda *s: torch.randn(*s, device=DEV)
+    # ---- state space
+    inner, C = H * P, H * P + 2 * G * N
+    proj = gen(T, 2 * inner + 2 * G * N + H).bfloat16()
+    conv_w, conv_b = gen(C, taps) * 0.5, gen(C) * 0.1
+    a_log, dt_bias, d_skip = torch.log(torch.rand(H, device=DEV) * 0.9 + 0.05), gen(H) * 0.5 - 1, gen(H)
+    slot = -(-(inner * N + (taps - 1) * C) // 4) * 4
+    state = gen(B, slot) * 0.1
+    norm_w = torch.rand(inner, device=DEV) + 0.5
+    xbc, dd = k.ssm_prepare(proj, conv_w, conv_b, a_log, dt_bias, ctx, state, inner * N, H, G, N, P, taps)
+    y = k.ssm_scan(xbc, dd, d_skip, ctx, state, H, G, N, P)
+    rows = [("ssm_prepare", lambda: k.ssm_prepare(proj, conv_w, conv_b, a_log, dt_bias, ctx, state, inner * N, H, G, N, P, taps),
+             T * (C + H) * 2 + T * (C + 2 * H) * 4 + B * (taps - 1) * C * 8),
+            ("ssm_scan", lambda: k.ssm_scan(xbc, dd, d_skip, ctx, state, H, G, N, P), 2 * B * inner * N * 4 + T * (C + 2 * H + inner) * 4),
+            ("gated_group_rmsnorm", lambda: k.gated_group_rmsnorm(y, proj[:, :inner], norm_w, 1e-6, G, torch.bfloat16),
+             T * inner * (4 + 2 + 2))]
+    # ---- delta rule: H heads of vdim P over keys of N values, G key heads
+    Cd = 2 * G * N + H * P
+    projd, ab = gen(T, Cd).bfloat16(), gen(T, 2 * H)
+    conv_d = gen(Cd, taps) * 0.5
+    slot_d = -(-(H * P * N + (taps - 1) * Cd) // 4) * 4
+    state_d = gen(B, slot_d) * 0.1
+    qkv, gb = k.delta_prepare(projd, ab, conv_d, a_log, dt_bias, ctx, state_d, H * P * N, H, G, N, P, taps)
+    o = k.delta_rule(qkv, gb, ctx, state_d, H, G, N, P)
+    gate, w_d = gen(T, inner).bfloat16(), torch.rand(P, device=DEV) + 0.5
+    rows += [("delta_prepare", lambda: k.delta_prepare(projd, ab, conv_d, a_log, dt_bias, ctx, state_d, H * P * N, H, G, N, P, taps),
+              T * Cd * 2 + T * 2 * H * 4 + T * (Cd + 2 * H) * 4 + B * (taps - 1) * Cd * 8),
+             ("delta_rule", lambda: k.delta_rule(qkv, gb, ctx, state_d, H, G, N, P), 2 * B * inner * N * 4 + T * (Cd + 2 * H + inner) * 4),
+             ("gated_rmsnorm", lambda: k.gated_rmsnorm(o, gate, w_d, 1e-6, H, P, torch.bfloat16), T * inner * (4 + 2 + 2))]
+    for name, fn, nbytes in rows:
+        if not name.startswith(a.only):
+            continue
+        us = _time_events(fn, a.replays, flush)
+        print(f"{name} B={B} qlen={q} heads={H} vdim={P} state={N} groups={G} taps={taps}: {us:.1f} us, {nbytes / 1e6:.1f} MB, "
+              f"{nbytes / us / 1e3:.0f} GB/s")
+    print("status", ctx.status.tolist())
+    return 0
+
+
+def _attn_masked(a) -> int:
+    """The tiled two-term attention kernel over bfloat16 pages with a sliding window (keys and values apart) and with
+    runs of positions, one more term in the denominator and values that are read from a second plane, at equal sizes;
+    then over pages of keys that are the values too (a latent of --hd values per token), with a learned term or none."""
+    B, q, c, nh, nkv, hd, ps, span = a.batch, a.qlen, a.ctx if a.ctx != 8192 or a.qlen == 1 else 0, a.nh, a.nkv, a.hd, a.page, a.span
+    ctx = _rows_ctx(B, q, c)
+    per = -(-(c + q) // ps)
+    flush = _flush()
+    grp = SimpleNamespace(block_tables=torch.randperm(B * per + 8, device=DEV)[:B * per].int().view(B, per).contiguous(), page_size=ps)
+    kv = torch.randn(B * per + 8, 2, nkv, ps, hd, device=DEV).bfloat16()
+    qq = torch.randn(B * q, nh * hd, device=DEV)
+    sinks0, sinks = torch.zeros(nh, device=DEV), torch.randn(nh, device=DEV)
+    seen = sum(min(p + 1, span) for p in range(c, c + q)) * B                 # keys in sight, windowed
+    seen_c = sum(p % span + 1 for p in range(c, c + q)) * B                  # in runs of positions
+    flops = lambda n: 4.0 * nh * hd * n
+    kvb = lambda n_rows: B * min(c + q, n_rows) * nkv * hd * 2 * 2
+    cases = [("window", lambda: k.paged_attention_wide(qq, kv, ctx, grp, nh, nkv, hd, hd ** -0.5, 30.0, span), seen, kvb(span + q)),
+             ("runs of positions, one more term", lambda: k.paged_attention_wide(qq, kv, ctx, grp, nh, nkv, hd, hd ** -0.5, 30.0, 0, chunk=span, sinks=sinks0),
+              seen_c, kvb((c + q - 1) % span + 1 if q == 1 else span))]
+    lat = torch.randn(B * per + 8, 1, 1, ps, hd, device=DEV).bfloat16()
+    every = sum(p + 1 for p in range(c, c + q)) * B
+    cases += [("latent, causal", lambda: k.paged_attention_wide(qq, lat, ctx, grp, nh, 1, hd, hd ** -0.5, 0.0, 0), every, B * (c + q) * hd * 2),
+              ("latent, causal, a learned term", lambda: k.paged_attention_wide(qq, lat, ctx, grp, nh, 1, hd, hd ** -0.5, 0.0, 0, sinks=sinks),
+               every, B * (c + q) * hd * 2)]
+    for name, fn, n, nbytes in cases:
+        if not name.startswith(a.only):
+            continue
+        us = _time_events(fn, a.replays, flush)
+        print(f"attn_masked {name} B={B} qlen={q} ctx={c} nh={nh} nkv={nkv} hd={hd} span={span}: {us:.1f} us, "
+              f"{flops(n) / us / 1e6:.1f} TFLOP/s of the attention's own flops, {nbytes / us / 1e3:.0f} GB/s of keys and values")
+    print("status", ctx.status.tolist())
+    return 0
+
+
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser(description=__doc__.split("\n\n")[0])
-    ap.add_argument("--kernel", required=True, choices=["attn_decode", "attn_prefill", "gemv", "gemm", "sample"])
+    ap.add_argument("--kernel", required=True, choices=["attn_decode", "attn_prefill", "gemv", "gemm", "sample", "recurrence", "attn_masked"])
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--ctx", type=int, default=8192, help="tokens already in the cache")
     ap.add_argument("--qlen", type=int, default=2048, help="tokens per row (attn_prefill)")
@@ -66,6 +183,10 @@ def main(argv=None) -> int:
     ap.add_argument("--nkv", type=int, default=8)
     ap.add_argument("--hd", type=int, default=64)
     ap.add_argument("--page", type=int, default=16)
+    ap.add_argument("--state", type=int, default=128, help="recurrence: rows of state per column (the delta rule's key size)")
+    ap.add_argument("--groups", type=int, default=8, help="recurrence: groups that share B and C (the delta rule's key heads)")
+    ap.add_argument("--taps", type=int, default=4)
+    ap.add_argument("--span", type=int, default=1024, help="attn_masked: the window, and the length of a run of positions")
     ap.add_argument("--splits", type=int, default=0, help="0: the engine's own choice")
     ap.add_argument("--M", type=int, default=8)
     ap.add_argument("--N", type=int, default=2048)
@@ -76,6 +197,10 @@ def main(argv=None) -> int:
     ap.add_argument("--launches", type=int, default=10, help="kernel launches per graph")
     ap.add_argument("--replays", type=int, default=5)
     a = ap.parse_args(argv)
+    if a.kernel == "recurrence":
+        return _recurrence(a)
+    if a.kernel == "attn_masked":
+        return _attn_masked(a)
     if a.kernel == "attn_decode":
         qkv, kv, ctx, grp = _attention_inputs(a, 1)
         splits = a.splits or k.decode_splits(a.batch, a.nkv, a.ctx + 1, a.hd)

@@ -352,6 +352,32 @@ def test_gated_product_with_gelu(dtype):
         assert torch.allclose(got, want, rtol=tol, atol=tol), (ff, block)
 
 
+def test_gelu_gated_product_in_the_products_epilogue():
+    """The decode product (at most 16 rows) and the tensor-memory product of prompt portions apply gelu(gate) * up
+    themselves over weights whose gate and up rows alternate in blocks of 128, as the separate kernel does."""
+    from fastmlx_b200 import kernels as k
+    dev = torch.device("cuda")
+    g = torch.Generator().manual_seed(12)
+    ff, width, block = 512, 256, 128
+    w = (torch.randn(2 * ff, width, generator=g) * 0.15).bfloat16()
+    rows = w.view(ff // block, 2, block, width).double()
+    wg, wu = rows[:, 0].reshape(ff, width), rows[:, 1].reshape(ff, width)
+    for M in (1, 5, 16, 384):
+        x = torch.randn(M, width, generator=g).bfloat16()
+        gate, up = (x.double() @ wg.T).bfloat16().double(), (x.double() @ wu.T).bfloat16().double()
+        want = ps.gelu_tanh(gate) * up
+        if M <= 16:
+            got = k.gemv(x.to(dev), w.to(dev), block=block, act="gelu_tanh")
+            silu = k.gemv(x.to(dev), w.to(dev), block=block)
+            assert torch.allclose(silu.cpu().double(), ps.silu(gate) * up, rtol=2e-2, atol=2e-2)     # the other gate is as it was
+        else:
+            got = k.gemm_tcgen05(x.to(dev), w.to(dev), epilogue=k.EPI_GELU_MUL)
+        assert got.shape == (M, ff)
+        assert torch.allclose(got.cpu().double(), want, rtol=2e-2, atol=2e-2), M
+        unfused = k.act_mul(k.linear(x.to(dev), w.to(dev), None, torch.bfloat16), "gelu_tanh", block)
+        assert (got.float() - unfused.float()).abs().max().item() <= 2.0 ** -7 * want.abs().max().item()
+
+
 # ----------------------------------------------------------------------------- the engine
 def _plain_greedy(cfg, W, prompt, n):
     toks, out, margins = list(prompt), [], []
