@@ -126,8 +126,8 @@ class StateSpaceConfig:
             raise ConfigError(f"sorupel: {where}: {c.heads} heads are no multiple of {c.groups} groups")
         if (c.heads * c.vdim) % c.norm_groups:
             raise ConfigError(f"sorupel: {where}: {c.heads * c.vdim} inner channels are no multiple of {c.norm_groups} norm_groups")
-        if c.conv > 16 or c.state > 256:
-            raise ConfigError(f"sorupel: {where}: at most 16 taps and a state of 256, got conv={c.conv}, state={c.state}")
+        if c.conv > 16 or c.state > 1024:
+            raise ConfigError(f"sorupel: {where}: at most 16 taps and a state of 1,024, got conv={c.conv}, state={c.state}")
         return c
 
 

@@ -17,7 +17,7 @@ __global__ void __launch_bounds__(LRP_THREADS)
 latent_rope_prepare_kernel(const TQ* q, long long q_stride, const float* dkv, long long dkv_stride, const int* positions,
                            const float* __restrict__ inv_freq, const float* __restrict__ norm_w, float eps,
                            const long long* slot_mapping, T* kv, long long max_rows, float* q_lat, int H, int D, int R,
-                           int r, int* status) {
+                           int r, int q_off, int* status) {
   extern __shared__ float sc[];                  // [R/2] sines, [R/2] cosines
   pdl_wait();
   pdl_trigger();
@@ -39,14 +39,15 @@ latent_rope_prepare_kernel(const TQ* q, long long q_stride, const float* dkv, lo
   ss = block_sum<LRP_THREADS>(ss);               // (its barriers also publish the sines and cosines)
   if (q_lat != nullptr) {
     const TQ* qp = q + (long long)t * q_stride;
-    float* out = q_lat + (long long)t * H * row;
+    const int q_row = q_off + R;                 // a head of q_lat: q_off values that are not written here, then the rotated part
+    float* out = q_lat + (long long)t * H * q_row;
     for (int i = threadIdx.x; i < H * half; i += blockDim.x) {
       const int h = i / half, j = i - h * half;
       const TQ* src = qp + (long long)h * (D + R) + D;
       float x, y;
       rope_pair(to_f(src[j]), to_f(src[j + half]), sn[j], cs[j], x, y);
-      out[(long long)h * row + r + j] = x;
-      out[(long long)h * row + r + half + j] = y;
+      out[(long long)h * q_row + q_off + j] = x;
+      out[(long long)h * q_row + q_off + half + j] = y;
     }
   }
   if (slot < 0) return;
@@ -63,12 +64,14 @@ latent_rope_prepare_kernel(const TQ* q, long long q_stride, const float* dkv, lo
 }  // namespace
 
 // q [T, >= H*(D+R)] of q_dtype (null with q_lat null: nothing of the queries is done); dkv [T, >= r+R] 32-bit and kv
-// (rows of r + R values of `dtype`, max_rows of them) may be null: a layer that reads another layer's cache.
+// (rows of r + R values of `dtype`, max_rows of them) may be null: a layer that reads another layer's cache.  q_lat
+// [T, H, q_off + R] takes the rotated query parts behind the first q_off values of a head (q_off < 0: r).
 FMX_EXPORT int fmx_latent_rope_prepare(const void* q, long long q_stride, int q_dtype, const float* dkv, long long dkv_stride,
                                        const int* positions, const float* inv_freq, const float* norm_w, float eps,
                                        const long long* slot_mapping, void* kv, long long max_rows, int dtype, float* q_lat,
-                                       int T, int H, int D, int R, int r, int* status, cudaStream_t stream) {
+                                       int T, int H, int D, int R, int r, int q_off, int* status, cudaStream_t stream) {
   if (T == 0) return 0;
+  if (q_off < 0) q_off = r;
   if (T < 0 || H <= 0 || D <= 0 || R < 0 || (R & 1) || r <= 0)
     return fmx_fail("fmx_latent_rope_prepare: bad sizes T=%d H=%d D=%d R=%d r=%d", T, H, D, R, r);
   if (R > 0 && inv_freq == nullptr) return fmx_fail("fmx_latent_rope_prepare: R=%d needs a frequency table", R);
@@ -80,7 +83,7 @@ FMX_EXPORT int fmx_latent_rope_prepare(const void* q, long long q_stride, int q_
 #define FMX_LRP(TQ, TKV)                                                                                               \
   fmx_launch(latent_rope_prepare_kernel<TQ, TKV>, dim3(T), dim3(LRP_THREADS), smem, stream, (const TQ*)q, q_stride, dkv, \
              dkv_stride, positions, inv_freq, norm_w, eps, slot_mapping, (TKV*)kv, max_rows, R > 0 ? q_lat : (float*)nullptr, \
-             H, D, R, r, status)
+             H, D, R, r, q_off, status)
   if (q_dtype == FMX_F32 && dtype == FMX_F32)
     FMX_LRP(float, float);
   else if (q_dtype == FMX_BF16 && dtype == FMX_BF16)

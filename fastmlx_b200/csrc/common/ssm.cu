@@ -264,7 +264,7 @@ FMX_EXPORT int fmx_ssm_scan(const float* xbc, const float* dd, const float* d_sk
                             const int* row_slot, float* state, long long slot_stride, float* out, int R, int H, int G, int N,
                             int P, int max_slots, int lanes, cudaStream_t stream) {
   if (R == 0) return 0;
-  if (R < 0 || H <= 0 || G <= 0 || H % G || N <= 0 || P <= 0 || N > 256)
+  if (R < 0 || H <= 0 || G <= 0 || H % G || N <= 0 || P <= 0 || N > 1024)
     return fmx_fail("fmx_ssm_scan: bad sizes R=%d H=%d G=%d N=%d P=%d", R, H, G, N, P);
   if (H > 65535 || R > 65535) return fmx_fail("fmx_ssm_scan: batch too large");
 #define FMX_SSM_SCAN(NPL, L, TB)                                                                                       \

@@ -424,12 +424,26 @@ WIDE_MAX_SPLITS = 16
 WIDE_HAS_SINKS = True            # the tiled kernel takes runs of positions and terms without a value too
 
 
-def wide_attention_splits(rows: int, nkv: int, keys: int, device=None) -> int:
-    """Blocks that share the keys of a one-token row out among them: enough for about two blocks per SM, each with
-    at least two 64-key tiles.  `keys`: the most keys a row sees (its window, or the longest context)."""
+def wide_attention_splits(rows: int, nkv: int, keys: int, device=None, hd: int = 64) -> int:
+    """Blocks that share the keys of a one-token row out among them.  `keys`: the most keys a row sees (its window, its
+    run of positions, or the longest context).  A grid that fills the GPU twice over as it is stays whole.  Else the
+    count s <= 16 (each share at least two 64-key tiles) with the shortest estimate waves(s) x (tiles / s + 2): the
+    grid's blocks run in waves of as many as are resident at once (one per SM with heads wider than 128, whose tiles
+    fill the shared memory; two otherwise), and a block costs its share of the tiles plus a fixed part.  Measured at
+    64 rows over one kv head of 256 values behind 4,096 keys: 5 shares (320 blocks, a second wave of 24) 288 us,
+    2 shares (128 blocks) 241 us; 32 rows: 10 shares 140 us, 4 shares 134 us; 16 rows: 16 shares 104 us, 9 shares 79 us."""
     tiles = -(-max(1, int(keys)) // 64) + 1
-    want = -(-2 * num_sms(device) // max(1, rows * nkv))
-    return max(1, min(want, tiles // 2, WIDE_MAX_SPLITS))
+    grid = max(1, rows * nkv)
+    sms = num_sms(device)
+    if grid >= 2 * sms:
+        return 1
+    slots = sms * (1 if hd > 128 else 2)
+    best, best_cost = 1, None
+    for s in range(1, max(1, min(tiles // 2, WIDE_MAX_SPLITS)) + 1):
+        cost = -(-grid * s // slots) * (-(-tiles // s) + 2)
+        if best_cost is None or cost < best_cost:
+            best, best_cost = s, cost
+    return best
 
 
 def wide_attention_takes(q, kv, hd, vd, out=None) -> bool:
@@ -488,7 +502,7 @@ def _paged_attention_wide(q, kv, ctx, group, nh, nkv, hd, scale, softcap, window
         return out
     longest = ctx.max_ctx_after if ctx.all_decode else ctx.decode_max_ctx
     keys = min(window + keep_first, longest) if window > 0 else (min(chunk, longest) if chunk > 0 else longest)
-    splits = wide_attention_splits(d, nkv, keys, q.device)
+    splits = wide_attention_splits(d, nkv, keys, q.device, hd)
     if splits > 1 and d * nh * splits * (hd + 2) > ATTN_SCRATCH_FLOATS:
         splits = 1
     if ctx.all_decode:
@@ -569,14 +583,17 @@ def embed_bigram(ids, table, bigram, ctx, state, buckets: int, mul_prev: int, mu
     return out
 
 
-def latent_rope_prepare(q, dkv, positions, inv_freq, norm_w, eps, slot_mapping, kv, q_lat, H, D, R, r, status) -> None:
+def latent_rope_prepare(q, dkv, positions, inv_freq, norm_w, eps, slot_mapping, kv, q_lat, H, D, R, r, status,
+                        q_offset: int | None = None) -> None:
     """Latent attention with a rotated key part: a token's down-projection dkv[t, :r+R] (32-bit; rows may be a slice)
     becomes its cache row [rmsnorm(dkv[:r]) * norm_w | dkv[r:] rotated] at slot_mapping[t] of `kv` (rows of r + R
     values), and the rotated parts of its query heads (q[t, h, D:D+R], pairs (i, i + R/2)) go, rotated, to
-    q_lat[t, h, r:r+R] in 32-bit.  dkv / kv None: a layer that reads another's cache stores nothing."""
+    q_lat[t, h, r:r+R] in 32-bit (with `q_offset` o: q_lat is [T, H * (o + R)] and takes them at [t, h, o:o+R]).
+    dkv / kv None: a layer that reads another's cache stores nothing."""
     _need_cuda(q, dkv, positions, inv_freq, norm_w, slot_mapping, kv, q_lat)
     assert q.dim() == 2 and q.stride(1) == 1 and q_lat.dtype == torch.float32 and q_lat.is_contiguous()
-    assert q_lat.shape == (q.shape[0], H * (r + R))
+    q_off = int(r if q_offset is None else q_offset)
+    assert q_lat.shape == (q.shape[0], H * (q_off + R))
     store = kv is not None and dkv is not None
     if store:
         assert dkv.dtype == torch.float32 and dkv.stride(1) == 1 and kv.is_contiguous() and kv.numel() % (r + R) == 0
@@ -586,7 +603,7 @@ def latent_rope_prepare(q, dkv, positions, inv_freq, norm_w, eps, slot_mapping, 
     call("common", "fmx_latent_rope_prepare", q.data_ptr(), q.stride(0), _dt(q), _ptr(dkv) if store else None,
          dkv.stride(0) if store else 0, positions.data_ptr(), _ptr(inv_freq), _ptr(norm_w) if store else None, float(eps),
          _ptr(slot_mapping) if store else None, _ptr(kv) if store else None, kv.numel() // (r + R) if store else 0,
-         _dt(kv) if store else _dt(q), q_lat.data_ptr(), q.shape[0], H, D, R, r, _ptr(status), _stream())
+         _dt(kv) if store else _dt(q), q_lat.data_ptr(), q.shape[0], H, D, R, r, q_off, _ptr(status), _stream())
 
 
 def ssm_prepare(proj, conv_w, conv_b, a_log, dt_bias, ctx, state, conv_off, H, G, N, P, taps):

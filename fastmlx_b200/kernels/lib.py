@@ -54,7 +54,7 @@ _SIGNATURES = {
                                           _I, _P, _I, _I, _P, _L, _I, _P, _I, _P],
         "fmx_qk_prepare_whole": [_P, _L, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _F, _I, _L, _I, _I, _P, _P, _P, _I,
                                  _P, _P],
-        "fmx_latent_rope_prepare": [_P, _L, _I, _P, _L, _P, _P, _P, _F, _P, _P, _L, _I, _P, _I, _I, _I, _I, _I, _P, _P],
+        "fmx_latent_rope_prepare": [_P, _L, _I, _P, _L, _P, _P, _P, _F, _P, _P, _L, _I, _P, _I, _I, _I, _I, _I, _I, _P, _P],
         "fmx_ssm_prepare": [_P, _L, _P, _P, _P, _P, _P, _P, _P, _P, _L, _L, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _I, _P, _P],
         "fmx_ssm_scan": [_P, _P, _P, _P, _P, _P, _L, _P, _I, _I, _I, _I, _I, _I, _I, _P],
         "fmx_gated_group_rmsnorm": [_P, _P, _L, _P, _P, _L, _I, _I, _I, _F, _I, _P],

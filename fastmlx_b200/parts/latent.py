@@ -103,6 +103,10 @@ class LatentAttention(Mixer):
         self.ukv = None
         if not self.direct and rt.dtype == torch.bfloat16 and self.hd == self.vd and self.hd % 16 == 0 and self.hd <= 256 and rt.device.type == "cuda":
             self.ukv = torch.cat([uk.reshape(self.nh * self.hd, self.kv_rank), self.uv.view(self.nh * self.vd, self.kv_rank)], 0).contiguous()
+        # the direct form: a head's key is [W_uk,h c | rotated part], as wide as its query; values are padded to that width
+        wide = self.hd + self.rot
+        if self.direct and rt.dtype == torch.bfloat16 and wide % 16 == 0 and wide <= 256 and self.vd <= wide and rt.device.type == "cuda":
+            self.ukv = torch.cat([uk.reshape(self.nh * self.hd, self.kv_rank), self.uv.view(self.nh * self.vd, self.kv_rank)], 0).contiguous()
 
     def weight_bytes(self):
         return super().weight_bytes() + (self.uk_t.numel() + self.uv.numel()) * self.uk_t.element_size()
@@ -118,12 +122,21 @@ class LatentAttention(Mixer):
         q = self.uq.forward(x)                                                   # [T, H * (dim + R)]
         down = self.down.forward(x, out_dtype=torch.float32) if self.down is not None else None
         store = cache.writable and not self.share_kv
-        q_lat = torch.empty((T, self.nh * self.row), dtype=torch.float32, device=x.device)
+        long = (self.ukv is not None and not ctx.all_decode and ctx.max_q_len >= self.LONG_PORTION
+                and cache.kv.dtype == torch.bfloat16 and hasattr(k, "paged_attention_wide"))
+        # a long portion carries its rotated query parts to [T, H, dim + R] instead: the heads' own keys are read out
+        lat_r = self.hd if long else r
+        q_lat = torch.empty((T, self.nh * (lat_r + R)), dtype=torch.float32, device=x.device)
         # the latent's norm and the rotation of the shared key part into the token's cache row; the queries'
         # rotated parts into the places behind their latent parts
         k.latent_rope_prepare(q, down[:, :self.row] if store else None, ctx.positions, self.inv_freq, self.c_norm, self.eps,
                               g.slot_mapping if store else None, cache.kv if store else None, q_lat, self.nh, self.hd, R, r,
-                              ctx.status)
+                              ctx.status, q_offset=lat_r)
+        if long:
+            heads = self.attend_long_direct(q, q_lat, ctx, cache, g)
+            if self.has_gate:
+                k.sigmoid_gate(heads, down[:, 0 if self.share_kv else self.row:], self.gate_group)
+            return self.o.forward(heads)
         k.head_linear(q, self.uk_t, torch.float32, x_head_stride=self.hd + R, out=q_lat, out_head_stride=self.row)
         opts = dict(sinks=self.sinks) if self.sinks is not None else {}
         wide = getattr(k, "wide_attention_takes", None) if (not opts or getattr(k, "WIDE_HAS_SINKS", False)) else None
@@ -166,6 +179,50 @@ class LatentAttention(Mixer):
         if self.has_gate:
             k.sigmoid_gate(heads, down[:, self.q_rank + self.kv_rank:], self.vd)
         return self.o.forward(heads)
+
+    def pages_in_sight(self, ctx, g):
+        """(row, block) of every page of positions that a row of this step may see, as device index vectors."""
+        ps = g.page_size
+        rows, blks = [], []
+        for r in range(ctx.R):
+            c = ctx.h_row_ctx[r]
+            n = ctx.h_row_start[r + 1] - ctx.h_row_start[r]
+            if ctx.h_row_slot[r] < 0 or n <= 0:
+                continue
+            lo = max(0, c - self.window + 1) if self.window > 0 else 0
+            for b in range(lo // ps, (c + n - 1) // ps + 1):
+                rows.append(r)
+                blks.append(b)
+        # one copy from pinned memory, so that the host does not fall into step with the device
+        both = torch.tensor([rows, blks], dtype=torch.long, pin_memory=True).to(g.block_tables.device, non_blocking=True)
+        return both[0], both[1], len(rows)
+
+    def attend_long_direct(self, q, q_wide, ctx, cache, g):
+        """The direct form over a long portion: per head, keys [W_uk,h c | the row's rotated part] and values W_uv,h c
+        (padded with zeros to the keys' width, which the tiled kernel wants equal) of every page in sight, read out of
+        the cached rows into pages that live for the step.  q [T, H * (dim + R)] as projected; q_wide (32-bit, same
+        shape) holds the rotated query parts already and takes the unrotated ones here.  -> [T, H * vdim]."""
+        from types import SimpleNamespace
+        k, ps = self.rt.k, g.page_size
+        T, H, D, R, Dv, r = q.shape[0], self.nh, self.hd, self.rot, self.vd, self.kv_rank
+        E = D + R
+        rows_t, blks_t, n = self.pages_in_sight(ctx, g)
+        pages = g.block_tables[rows_t, blks_t].long().clamp_(min=0)
+        cached = cache.kv.view(cache.kv.shape[0], ps, self.row)[pages]           # [pages in sight, page, kv_rank + R]
+        kv = k.linear(cached[..., :r].reshape(-1, r), self.ukv, None, torch.bfloat16)       # [n * page, H * (dim + vdim)]
+        own = torch.zeros((n, 2, H, ps, E), dtype=torch.bfloat16, device=q.device)
+        own[:, 0, :, :, :D] = kv[:, :H * D].view(n, ps, H, D).permute(0, 2, 1, 3)
+        if R:
+            own[:, 0, :, :, D:] = cached[..., r:].unsqueeze(1)
+        own[:, 1, :, :, :Dv] = kv[:, H * D:].view(n, ps, H, Dv).permute(0, 2, 1, 3)
+        table = torch.full_like(g.block_tables, -1)
+        table[rows_t, blks_t] = torch.arange(n, dtype=torch.int32, device=q.device)
+        group = SimpleNamespace(block_tables=table, page_size=ps, window=self.window)
+        ctx.scratch.setdefault("pages of a step", []).append(group)       # kept for the step: its identity keys cached views
+        q_wide.view(T, H, E)[..., :D] = q.view(T, H, E)[..., :D]
+        opts = dict(sinks=self.sinks) if self.sinks is not None else {}
+        out = k.paged_attention_wide(q_wide, own, ctx, group, H, H, E, self.scale, 0.0, self.window, **opts)
+        return out.view(T, H, E)[..., :Dv].reshape(T, H * Dv)
 
     def attend_long(self, cq, ctx, cache, g):
         """Keys and values of every position a row of this step may see, read out of the cached latents into pages

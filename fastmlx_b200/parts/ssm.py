@@ -34,8 +34,8 @@ class StateSpaceMixer(Mixer):
             raise ValueError(f"{heads * vdim} channels are no multiple of {norm_groups} parts")
         if not 1 <= taps <= 16:
             raise ValueError(f"a short convolution has 1 to 16 taps, not {taps}")
-        if state > 256:
-            raise ValueError(f"the recurrence keeps up to 256 rows of state per column, not {state}")
+        if state > 1024:
+            raise ValueError(f"the recurrence keeps up to 1,024 rows of state per column, not {state}")
         self.H, self.P, self.N, self.G = int(heads), int(vdim), int(state), int(groups)
         self.norm_groups, self.taps, self.eps = int(norm_groups), int(taps), float(norm_eps)
         self.inner = self.H * self.P

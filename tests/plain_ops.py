@@ -408,12 +408,13 @@ def embed_bigram(ids, table, bigram, ctx, state, buckets, mul_prev, mul_cur):
     return out
 
 
-def latent_rope_prepare(q, dkv, positions, inv_freq, norm_w, eps, slot_mapping, kv, q_lat, H, D, R, r, status):
+def latent_rope_prepare(q, dkv, positions, inv_freq, norm_w, eps, slot_mapping, kv, q_lat, H, D, R, r, status, q_offset=None):
     T = q.shape[0]
     row = r + R
     if R:
+        off = r if q_offset is None else q_offset
         qr = q.reshape(T, H, D + R)[:, :, D:].to(F64)
-        q_lat.view(T, H, row)[:, :, r:] = _rotate(qr, positions, inv_freq, R, False).to(q_lat.dtype)
+        q_lat.view(T, H, off + R)[:, :, off:] = _rotate(qr, positions, inv_freq, R, False).to(q_lat.dtype)
     if kv is None or dkv is None:
         return
     c = dkv[:, :r].to(F64)

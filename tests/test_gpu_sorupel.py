@@ -259,7 +259,7 @@ def test_latent_attention_far_key_first_tokens_and_learned_sink(tmp_path, dtype,
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("shape", [(4, 10, 12, 2, 2, 3), (1, 64, 8, 1, 1, 4), (6, 32, 64, 3, 4, 2), (3, 7, 100, 1, 3, 5),
-                                   (4, 5, 9, 4, 1, 1)], ids=lambda s: "x".join(map(str, s)))
+                                   (4, 5, 9, 4, 1, 1), (2, 8, 300, 1, 1, 2)], ids=lambda s: "x".join(map(str, s)))
 def test_state_space_mixer_alone(tmp_path, dtype, shape):
     """(heads, vdim, state, groups, norm parts, taps).  Three requests in portions of one, two and many tokens; one
     head decays so slowly that the first token still counts after 300; then the slots are given back and taken again by

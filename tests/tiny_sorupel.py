@@ -63,7 +63,7 @@ S3 = {
     "architecture": "Sorupel", "vocab": 130, "width": 128, "norm": {"eps": 1e-4}, "embedding": bigram(1000, 3, 1),
     "layers": [
         layer("latent_attention", latent(4, 32, 16, 32, 96, 0.14, 1000000.0), ff=256),
-        layer("attention", attention(8, 2, 64, 0.125, softcap=12.0, chunk=100, rot=(16, 20000.0)), ff=128),
+        layer("attention", attention(8, 2, 64, 0.125, softcap=12.0, chunk=100, rot=(16, 30000.0)), ff=128),
         layer("mamba2", mamba(6, 32, 64, 3, 4, 2), ff=128),
         layer("latent_attention", latent(2, 48, 16, 64, 48, 0.1, 777.0)),
         layer("latent_attention", latent(8, 16, 16, 16, 96, 0.2, 1000000.0, kv_from=0), ff=96),
