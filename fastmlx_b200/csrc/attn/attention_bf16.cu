@@ -49,6 +49,11 @@ constexpr int TILE = BN * ROW;           // elements of one K (or V) tile
 constexpr int THREADS = 128;
 constexpr int PREFILL_STAGES = HD <= 128 ? 3 : 2;
 constexpr int DECODE_STAGES = HD <= 128 ? 3 : 2;
+// The form with 32-bit queries holds 2 x KSTEPS x 4 registers of query fragments beside NT_O x 4 of output: past a
+// head size of 128 that is more than a thread has, so the fragments live in shared memory behind the tiles.
+constexpr bool Q_SHARED = HD > 128;
+constexpr size_t prefill_smem() { return (size_t)PREFILL_STAGES * 2 * TILE * 2; }
+constexpr size_t wide_smem() { return prefill_smem() + (Q_SHARED ? (size_t)(THREADS / 32) * 2 * KSTEPS * 32 * 16 : 0); }
 constexpr int MO_ROW = HD + 4;           // floats in a row of a warp's partial output: heads 2t and 2t + 2 on other banks
 // Groups of 16 keys in a warp's decode tile.  Grids of few blocks (batch 1 to 4 with 8 kv heads) are bound by the
 // chain of one pass of the loop, not by bandwidth: there a pass takes 32 keys per warp where two blocks of that
@@ -208,6 +213,29 @@ __device__ __forceinline__ void qk_tile(float (&s)[NT][4], const unsigned (&q)[K
         mma_bf16(s[2 * jp], q2[k], b0, b1);
         mma_bf16(s[2 * jp + 1], q2[k], b2, b3);
       }
+    }
+  }
+}
+
+// The same with the queries' two terms read from shared memory, where this warp left its fragments as
+// qs[term][k-step][lane] (16 bytes each): heads wider than 128 have no registers left for them beside the output.
+template <int NT>
+__device__ __forceinline__ void qk_tile_shared(float (&s)[NT][4], const uint4* qs, const bf16* ks, int key_row0) {
+  const int lane = threadIdx.x & 31;
+  const int mi = lane >> 3, ri = lane & 7;
+#pragma unroll 4
+  for (int k = 0; k < KSTEPS; ++k) {
+    const uint4 u = qs[k * 32 + lane], u2 = qs[(KSTEPS + k) * 32 + lane];
+    const unsigned q[4] = {u.x, u.y, u.z, u.w}, q2[4] = {u2.x, u2.y, u2.z, u2.w};
+#pragma unroll
+    for (int jp = 0; jp < NT / 2; ++jp) {
+      unsigned b0, b1, b2, b3;
+      const bf16* p = ks + (key_row0 + 16 * jp + (mi >> 1) * 8 + ri) * ROW + 16 * k + (mi & 1) * 8;
+      ldmatrix_x4(b0, b1, b2, b3, p);
+      mma_bf16(s[2 * jp], q, b0, b1);
+      mma_bf16(s[2 * jp + 1], q, b2, b3);
+      mma_bf16(s[2 * jp], q2, b0, b1);
+      mma_bf16(s[2 * jp + 1], q2, b2, b3);
     }
   }
 }
@@ -516,8 +544,12 @@ attn_prefill_kernel(const void* __restrict__ q_any, long long q_stride, const bf
   // A row of one token has at most 16 packed rows (its heads): they fit one warp's MMA rows.  Then all four warps take
   // those rows and a quarter of every key tile each (16 keys), and their parts are added up at the end, instead of
   // three warps standing by while the first walks every key.
-  const bool one_token = WIDE && q_len == 1 && rep <= 16;
-  const int wrow = one_token ? 0 : warp * 16;      // the first packed row of this warp within the block's tile
+  // With 17 to 32 heads they fit two warps' rows: two pairs of warps, each pair with half of every key tile.
+  const bool one_token = WIDE && q_len == 1 && rep <= 32;
+  const int kparts = rep <= 16 ? 4 : 2;            // the warps that share a tile's keys out among them
+  const int ksub = 4 / kparts;                     // groups of 16 keys of a tile that fall to one warp
+  const int kpart = warp & (kparts - 1);
+  const int wrow = one_token ? (warp / kparts) * 16 : warp * 16;   // the first packed row of this warp within the block's tile
   const Cache c{kv, block_tables + (long long)r * bt_stride, bt_stride, nkv, page_size, num_pages,
                 page_shift_of(page_size), WIDE ? keys_only : 0};
   const int keep = WIDE && window > 0 ? keep_first : 0;      // a request's first tokens that stay visible behind the window
@@ -539,8 +571,28 @@ attn_prefill_kernel(const void* __restrict__ q_any, long long q_stride, const bf
     lo[x] = lo_of(ctx + tok[x]);
   }
   // query fragments, straight from global memory
-  unsigned qf[KSTEPS][4];
-  unsigned qf2[WIDE ? KSTEPS : 1][4];
+  constexpr bool QS = WIDE && Q_SHARED;
+  unsigned qf[QS ? 1 : KSTEPS][4];
+  unsigned qf2[WIDE && !QS ? KSTEPS : 1][4];
+  uint4* qs = reinterpret_cast<uint4*>(smem_raw + prefill_smem()) + (size_t)warp * 2 * KSTEPS * 32;
+  if constexpr (QS) {
+    for (int k = 0; k < KSTEPS; ++k) {
+      unsigned a[4], a2[4];
+#pragma unroll
+      for (int x = 0; x < 2; ++x) {
+        const float* qp = reinterpret_cast<const float*>(q_any) + (long long)(t0 + tok[x]) * q_stride + (long long)head[x] * HD + 16 * k + 2 * tq;
+        const float2 u = rvalid[x] ? *reinterpret_cast<const float2*>(qp) : make_float2(0.f, 0.f);
+        const float2 v = rvalid[x] ? *reinterpret_cast<const float2*>(qp + 8) : make_float2(0.f, 0.f);
+        a[x] = pack_bf16(u.x, u.y);
+        a[x + 2] = pack_bf16(v.x, v.y);
+        a2[x] = pack_bf16_rest(u.x, u.y);
+        a2[x + 2] = pack_bf16_rest(v.x, v.y);
+      }
+      qs[k * 32 + lane] = make_uint4(a[0], a[1], a[2], a[3]);
+      qs[(KSTEPS + k) * 32 + lane] = make_uint4(a2[0], a2[1], a2[2], a2[3]);
+    }
+    __syncwarp();
+  } else {
 #pragma unroll
   for (int k = 0; k < KSTEPS; ++k)
 #pragma unroll
@@ -559,6 +611,7 @@ attn_prefill_kernel(const void* __restrict__ q_any, long long q_stride, const bf
         qf[k][x + 2] = rvalid[x] ? *reinterpret_cast<const unsigned*>(qp + 8) : 0u;
       }
     }
+  }
   const bool capped = WIDE && softcap > 0.f;
   const float cap_l2 = softcap * LOG2E, scale_cap = capped ? scale / softcap : 0.f;
 
@@ -619,15 +672,18 @@ attn_prefill_kernel(const void* __restrict__ q_any, long long q_stride, const bf
     const bf16* vs = stage_v(it % PREFILL_STAGES);
     if (WIDE && prow0 + wrow >= n_packed) continue;             // a warp without a row only copies
     if (one_token) {
-      // this warp's quarter of the tile: 16 keys against the row's heads
+     // this warp's part of the tile, 16 keys at a time against its 16 of the row's heads
+     for (int sub = 0; sub < ksub; ++sub) {
+      const int krow = 16 * (kpart * ksub + sub);
       float s2[2][4];
 #pragma unroll
       for (int j = 0; j < 2; ++j)
 #pragma unroll
         for (int e = 0; e < 4; ++e) s2[j][e] = 0.f;
-      qk_tile<2, WIDE>(s2, qf, ks, 16 * warp, qf2);
+      if constexpr (QS) qk_tile_shared<2>(s2, qs, ks, krow);
+      else qk_tile<2, WIDE>(s2, qf, ks, krow, qf2);
       float alpha[2];
-      const int qk0 = tile_key(tile0 + it) + 16 * warp;
+      const int qk0 = tile_key(tile0 + it) + krow;
       if (kept_tile) {
         if (capped) softmax_step<2, true, true>(s2, m, l, alpha, sl2, qk0, lim_kept, lo_kept, cap_l2, scale_cap);
         else softmax_step<2, true>(s2, m, l, alpha, sl2, qk0, lim_kept, lo_kept);
@@ -638,7 +694,8 @@ attn_prefill_kernel(const void* __restrict__ q_any, long long q_stride, const bf
         o[n][0] *= alpha[0]; o[n][1] *= alpha[0];
         o[n][2] *= alpha[1]; o[n][3] *= alpha[1];
       }
-      pv_tile<1, WIDE>(o, s2, vs, 16 * warp);
+      pv_tile<1, WIDE>(o, s2, vs, krow);
+     }
       continue;
     }
     float s[BN / 8][4];
@@ -646,7 +703,8 @@ attn_prefill_kernel(const void* __restrict__ q_any, long long q_stride, const bf
     for (int j = 0; j < BN / 8; ++j)
 #pragma unroll
       for (int e = 0; e < 4; ++e) s[j][e] = 0.f;
-    qk_tile<BN / 8, WIDE>(s, qf, ks, 0, qf2);
+    if constexpr (QS) qk_tile_shared<BN / 8>(s, qs, ks, 0);
+    else qk_tile<BN / 8, WIDE>(s, qf, ks, 0, qf2);
     float alpha[2];
     const int tk0 = tile_key(tile0 + it);
     const bool open = !kept_tile && warp_full && tk0 >= sure_lo && tk0 + BN - 1 <= sure_hi;
@@ -671,7 +729,7 @@ attn_prefill_kernel(const void* __restrict__ q_any, long long q_stride, const bf
   }
   cp_async_wait<0>();
   if (one_token) {
-    // the four warps' parts of the same rows, added up in warp order through the tiles' shared memory
+    // the warps' parts of the same rows, added up in warp order through the tiles' shared memory
     __syncthreads();
     float* red = reinterpret_cast<float*>(smem_raw);           // [4][16][HD + 2]
 #pragma unroll
@@ -686,14 +744,13 @@ attn_prefill_kernel(const void* __restrict__ q_any, long long q_stride, const bf
     __syncthreads();
     for (int idx = threadIdx.x; idx < rep * HD; idx += THREADS) {
       const int row = idx / HD, e = idx - row * HD;
+      const int w0 = (row >> 4) * kparts, wr = row & 15;     // the warps that hold this row, and its place in theirs
       float M = -INFINITY;
-#pragma unroll
-      for (int w = 0; w < 4; ++w) M = fmaxf(M, red[(w * 16 + row) * (HD + 2) + HD]);
+      for (int w = w0; w < w0 + kparts; ++w) M = fmaxf(M, red[(w * 16 + wr) * (HD + 2) + HD]);
       float L = 0.f, O = 0.f;
       if (M != -INFINITY) {
-#pragma unroll
-        for (int w = 0; w < 4; ++w) {
-          const float* pw = red + (w * 16 + row) * (HD + 2);
+        for (int w = w0; w < w0 + kparts; ++w) {
+          const float* pw = red + (w * 16 + wr) * (HD + 2);
           const float f = fast_exp2(pw[HD] - M);
           L = fmaf(pw[HD + 1], f, L);
           O = fmaf(pw[e], f, O);
@@ -1182,7 +1239,7 @@ __global__ void attn_combine_kernel(const float* part_o, const float* part_ml, c
   }
 }
 
-constexpr size_t prefill_smem() { return (size_t)PREFILL_STAGES * 2 * TILE * sizeof(bf16); }
+
 constexpr size_t decode_smem(int kg = 1) {
   const size_t pipe = (size_t)DECODE_STAGES * 2 * 4 * 16 * kg * ROW * sizeof(bf16);
   const size_t merge = (size_t)(4 * 16 * MO_ROW + 4 * 16 * 2 + 16 * HD + 16 * 2) * sizeof(float);
@@ -1333,8 +1390,8 @@ FMX_EXPORT int fmx_attn_prefill_wide_masked(const float* q, long long q_stride, 
   static bool configured = false;
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(attn_prefill_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         (int)prefill_smem());
-    if (e != cudaSuccess) return fmx_fail("fmx_attn_prefill_wide: shared memory of %zu bytes refused: %s", prefill_smem(),
+                                         (int)wide_smem());
+    if (e != cudaSuccess) return fmx_fail("fmx_attn_prefill_wide: shared memory of %zu bytes refused: %s", wide_smem(),
                                           cudaGetErrorString(e));
     configured = true;
   }
@@ -1348,14 +1405,14 @@ FMX_EXPORT int fmx_attn_prefill_wide_masked(const float* q, long long q_stride, 
     if (scratch == nullptr || (long long)n_tokens * nh * n_splits * (HD + 2) > scratch_floats)
       return fmx_fail("fmx_attn_prefill_wide: the workspace is too small for %d shares of %d tokens", n_splits, n_tokens);
     dim3 grid(nkv, rows, (unsigned)n_splits);
-    attn_prefill_kernel<true><<<grid, THREADS, prefill_smem(), stream>>>(
+    attn_prefill_kernel<true><<<grid, THREADS, wide_smem(), stream>>>(
         q, q_stride, (const bf16*)kv, block_tables, bt_stride, row_start, row_ctx, (bf16*)out, nh, nkv, page_size,
         num_pages, scale, window, status, softcap, out_stride, positions, scratch, n_splits, keep_first, keys_only, chunk, sinks);
     FMX_LAUNCH_CHECK();
     return 0;
   }
   dim3 grid(nkv, rows, (unsigned)tiles);
-  attn_prefill_kernel<true><<<grid, THREADS, prefill_smem(), stream>>>(
+  attn_prefill_kernel<true><<<grid, THREADS, wide_smem(), stream>>>(
       q, q_stride, (const bf16*)kv, block_tables, bt_stride, row_start, row_ctx, (bf16*)out, nh, nkv, page_size,
       num_pages, scale, window, status, softcap, out_stride, positions, (float*)nullptr, 1, keep_first, keys_only, chunk, sinks);
   FMX_LAUNCH_CHECK();

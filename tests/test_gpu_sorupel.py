@@ -257,6 +257,32 @@ def test_latent_attention_far_key_first_tokens_and_learned_sink(tmp_path, dtype,
     assert (want[0][p, D:2 * D] / gate[D:] - share * c1).abs().max().item() < 0.05 and 0.5 < share < 0.95
 
 
+@pytest.mark.parametrize("kind,mixer", [
+    ("latent_attention", ts.latent(20, 16, 16, 16, 176, 0.2, 5000.0)),       # cache rows of 192 values, 20 heads on them
+    ("latent_attention", ts.latent(32, 16, 32, 16, 224, 0.15, 5000.0)),      # rows of 256, 32 heads
+    ("latent_attention", ts.latent(12, 16, 16, 16, 128, 0.2, 5000.0)),       # rows of 144, heads that fit one warp's rows
+    ("attention", ts.attention(24, 1, 64, 0.3, softcap=20.0, chunk=150, rot=(32, 3000.0))),
+    ("attention", ts.attention(40, 2, 64, 0.3, chunk=90, rot=(16, 3000.0))),
+    ("attention", ts.attention(64, 2, 32, 0.3, softcap=20.0, chunk=400)),
+], ids=["latent-20x192", "latent-32x256", "latent-12x144", "attention-24:1", "attention-40:2", "attention-64:2"])
+def test_single_tokens_with_many_heads_on_one_key_head(tmp_path, kind, mixer):
+    """Single tokens of 17 to 32 query heads per key head share a tile's keys out over pairs of warps, and cache rows
+    wider than 128 values keep the queries' terms in shared memory: three requests of unequal length, decoded one by
+    one side by side behind prompts, short enough for one block per row and long enough for shares of the keys."""
+    width = 96
+    rig = Rig(tmp_path, kind, mixer, {}, width, "bfloat16", max_tokens=1024)
+    g = torch.Generator().manual_seed(11)
+    lens = [420, 37, 150]
+    hs = [_rounded(torch.randn(n, width, generator=g, dtype=torch.float64)) for n in lens]
+    plain = ps.latent_attention if kind == "latent_attention" else ps.chunked_attention
+    want = [plain(h, rig.W, mixer, rig.eps) for h in hs]
+    want = [w[0] if isinstance(w, tuple) else w for w in want]
+    steps = [[380, 3, 120]] + [[1, 1, 1]] * 30 + [[1, 0, 0]] * 10
+    got = rig.feed(hs, steps)
+    for a, b in zip(got, want):
+        _close(a, b[:a.shape[0]], 3e-2)
+
+
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("shape", [(4, 10, 12, 2, 2, 3), (1, 64, 8, 1, 1, 4), (6, 32, 64, 3, 4, 2), (3, 7, 100, 1, 3, 5),
                                    (4, 5, 9, 4, 1, 1), (2, 8, 300, 1, 1, 2)], ids=lambda s: "x".join(map(str, s)))
