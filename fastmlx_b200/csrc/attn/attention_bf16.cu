@@ -30,6 +30,7 @@
 // zero-filled in shared memory and masked, never read from the cache.
 #include <mutex>
 #include <math.h>
+#include <type_traits>
 #include "common.cuh"
 
 #ifndef FMX_HD
@@ -201,17 +202,22 @@ __device__ __forceinline__ void qk_tile(float (&s)[NT][4], const unsigned (&q)[K
   const int mi = lane >> 3, ri = lane & 7;
 #pragma unroll
   for (int k = 0; k < KSTEPS; ++k) {
+    // two terms: every column tile takes the first term before any takes the second, so that the two products into
+    // one accumulator stand NT instructions apart instead of two (the order of sums in an accumulator stays)
+    unsigned b[NT / 2][4];
 #pragma unroll
     for (int jp = 0; jp < NT / 2; ++jp) {
-      unsigned b0, b1, b2, b3;
       // matrices: (keys 16jp.., hd 16k), (same keys, hd 16k+8), (keys 16jp+8.., hd 16k), (.., hd 16k+8)
       const bf16* p = ks + (key_row0 + 16 * jp + (mi >> 1) * 8 + ri) * ROW + 16 * k + (mi & 1) * 8;
-      ldmatrix_x4(b0, b1, b2, b3, p);
-      mma_bf16(s[2 * jp], q[k], b0, b1);
-      mma_bf16(s[2 * jp + 1], q[k], b2, b3);
-      if (SPLIT) {
-        mma_bf16(s[2 * jp], q2[k], b0, b1);
-        mma_bf16(s[2 * jp + 1], q2[k], b2, b3);
+      ldmatrix_x4(b[jp][0], b[jp][1], b[jp][2], b[jp][3], p);
+      mma_bf16(s[2 * jp], q[k], b[jp][0], b[jp][1]);
+      mma_bf16(s[2 * jp + 1], q[k], b[jp][2], b[jp][3]);
+    }
+    if (SPLIT) {
+#pragma unroll
+      for (int jp = 0; jp < NT / 2; ++jp) {
+        mma_bf16(s[2 * jp], q2[k], b[jp][0], b[jp][1]);
+        mma_bf16(s[2 * jp + 1], q2[k], b[jp][2], b[jp][3]);
       }
     }
   }
@@ -227,15 +233,18 @@ __device__ __forceinline__ void qk_tile_shared(float (&s)[NT][4], const uint4* q
   for (int k = 0; k < KSTEPS; ++k) {
     const uint4 u = qs[k * 32 + lane], u2 = qs[(KSTEPS + k) * 32 + lane];
     const unsigned q[4] = {u.x, u.y, u.z, u.w}, q2[4] = {u2.x, u2.y, u2.z, u2.w};
+    unsigned b[NT / 2][4];
 #pragma unroll
     for (int jp = 0; jp < NT / 2; ++jp) {
-      unsigned b0, b1, b2, b3;
       const bf16* p = ks + (key_row0 + 16 * jp + (mi >> 1) * 8 + ri) * ROW + 16 * k + (mi & 1) * 8;
-      ldmatrix_x4(b0, b1, b2, b3, p);
-      mma_bf16(s[2 * jp], q, b0, b1);
-      mma_bf16(s[2 * jp + 1], q, b2, b3);
-      mma_bf16(s[2 * jp], q2, b0, b1);
-      mma_bf16(s[2 * jp + 1], q2, b2, b3);
+      ldmatrix_x4(b[jp][0], b[jp][1], b[jp][2], b[jp][3], p);
+      mma_bf16(s[2 * jp], q, b[jp][0], b[jp][1]);
+      mma_bf16(s[2 * jp + 1], q, b[jp][2], b[jp][3]);
+    }
+#pragma unroll
+    for (int jp = 0; jp < NT / 2; ++jp) {
+      mma_bf16(s[2 * jp], q2, b[jp][0], b[jp][1]);
+      mma_bf16(s[2 * jp + 1], q2, b[jp][2], b[jp][3]);
     }
   }
 }
@@ -264,17 +273,29 @@ __device__ __forceinline__ void pv_tile(float (&o)[NT_O][4], const float (&p)[2 
       a2[2] = pack_bf16_rest(p[2 * kk + 1][0], p[2 * kk + 1][1]);
       a2[3] = pack_bf16_rest(p[2 * kk + 1][2], p[2 * kk + 1][3]);
     }
+    // two pairs of output tiles at a time: with two terms, four products stand between the two into one accumulator
+    constexpr int PAIRS = NT_O / 2;
 #pragma unroll
-    for (int np = 0; np < NT_O / 2; ++np) {
-      unsigned b0, b1, b2, b3;
-      // matrices: (keys 16kk.., hd 16np), (keys 16kk+8.., hd 16np), (keys 16kk.., hd 16np+8), (keys 16kk+8.., hd 16np+8)
-      const bf16* ptr = vs + (key_row0 + 16 * kk + (mi & 1) * 8 + ri) * ROW + 16 * np + (mi >> 1) * 8;
-      ldmatrix_x4_trans(b0, b1, b2, b3, ptr);
-      mma_bf16(o[2 * np], a, b0, b1);
-      mma_bf16(o[2 * np + 1], a, b2, b3);
+    for (int np0 = 0; np0 < PAIRS; np0 += 2) {
+      unsigned b[2][4];
+#pragma unroll
+      for (int u = 0; u < 2; ++u) {
+        const int np = np0 + u;
+        if (np >= PAIRS) break;
+        // matrices: (keys 16kk.., hd 16np), (keys 16kk+8.., hd 16np), (keys 16kk.., hd 16np+8), (keys 16kk+8.., hd 16np+8)
+        const bf16* ptr = vs + (key_row0 + 16 * kk + (mi & 1) * 8 + ri) * ROW + 16 * np + (mi >> 1) * 8;
+        ldmatrix_x4_trans(b[u][0], b[u][1], b[u][2], b[u][3], ptr);
+        mma_bf16(o[2 * np], a, b[u][0], b[u][1]);
+        mma_bf16(o[2 * np + 1], a, b[u][2], b[u][3]);
+      }
       if (SPLIT) {
-        mma_bf16(o[2 * np], a2, b0, b1);
-        mma_bf16(o[2 * np + 1], a2, b2, b3);
+#pragma unroll
+        for (int u = 0; u < 2; ++u) {
+          const int np = np0 + u;
+          if (np >= PAIRS) break;
+          mma_bf16(o[2 * np], a2, b[u][0], b[u][1]);
+          mma_bf16(o[2 * np + 1], a2, b[u][2], b[u][3]);
+        }
       }
     }
   }
@@ -547,7 +568,6 @@ attn_prefill_kernel(const void* __restrict__ q_any, long long q_stride, const bf
   // With 17 to 32 heads they fit two warps' rows: two pairs of warps, each pair with half of every key tile.
   const bool one_token = WIDE && q_len == 1 && rep <= 32;
   const int kparts = rep <= 16 ? 4 : 2;            // the warps that share a tile's keys out among them
-  const int ksub = 4 / kparts;                     // groups of 16 keys of a tile that fall to one warp
   const int kpart = warp & (kparts - 1);
   const int wrow = one_token ? (warp / kparts) * 16 : warp * 16;   // the first packed row of this warp within the block's tile
   const Cache c{kv, block_tables + (long long)r * bt_stride, bt_stride, nkv, page_size, num_pages,
@@ -672,30 +692,33 @@ attn_prefill_kernel(const void* __restrict__ q_any, long long q_stride, const bf
     const bf16* vs = stage_v(it % PREFILL_STAGES);
     if (WIDE && prow0 + wrow >= n_packed) continue;             // a warp without a row only copies
     if (one_token) {
-     // this warp's part of the tile, 16 keys at a time against its 16 of the row's heads
-     for (int sub = 0; sub < ksub; ++sub) {
-      const int krow = 16 * (kpart * ksub + sub);
-      float s2[2][4];
+      // this warp's part of the tile (a quarter: 16 keys, or a half: 32) against its 16 of the row's heads
+      auto part = [&](auto groups) {
+        constexpr int NT = 2 * decltype(groups)::value;          // 8-key column tiles of the part
+        const int krow = 8 * NT * kpart;
+        float s2[NT][4];
 #pragma unroll
-      for (int j = 0; j < 2; ++j)
+        for (int j = 0; j < NT; ++j)
 #pragma unroll
-        for (int e = 0; e < 4; ++e) s2[j][e] = 0.f;
-      if constexpr (QS) qk_tile_shared<2>(s2, qs, ks, krow);
-      else qk_tile<2, WIDE>(s2, qf, ks, krow, qf2);
-      float alpha[2];
-      const int qk0 = tile_key(tile0 + it) + krow;
-      if (kept_tile) {
-        if (capped) softmax_step<2, true, true>(s2, m, l, alpha, sl2, qk0, lim_kept, lo_kept, cap_l2, scale_cap);
-        else softmax_step<2, true>(s2, m, l, alpha, sl2, qk0, lim_kept, lo_kept);
-      } else if (capped) softmax_step<2, true, true>(s2, m, l, alpha, sl2, qk0, lim, lo, cap_l2, scale_cap, keep);
-      else softmax_step<2, true>(s2, m, l, alpha, sl2, qk0, lim, lo, 0.f, 0.f, keep);
+          for (int e = 0; e < 4; ++e) s2[j][e] = 0.f;
+        if constexpr (QS) qk_tile_shared<NT>(s2, qs, ks, krow);
+        else qk_tile<NT, WIDE>(s2, qf, ks, krow, qf2);
+        float alpha[2];
+        const int qk0 = tile_key(tile0 + it) + krow;
+        if (kept_tile) {
+          if (capped) softmax_step<NT, true, true>(s2, m, l, alpha, sl2, qk0, lim_kept, lo_kept, cap_l2, scale_cap);
+          else softmax_step<NT, true>(s2, m, l, alpha, sl2, qk0, lim_kept, lo_kept);
+        } else if (capped) softmax_step<NT, true, true>(s2, m, l, alpha, sl2, qk0, lim, lo, cap_l2, scale_cap, keep);
+        else softmax_step<NT, true>(s2, m, l, alpha, sl2, qk0, lim, lo, 0.f, 0.f, keep);
 #pragma unroll
-      for (int n = 0; n < NT_O; ++n) {
-        o[n][0] *= alpha[0]; o[n][1] *= alpha[0];
-        o[n][2] *= alpha[1]; o[n][3] *= alpha[1];
-      }
-      pv_tile<1, WIDE>(o, s2, vs, krow);
-     }
+        for (int n = 0; n < NT_O; ++n) {
+          o[n][0] *= alpha[0]; o[n][1] *= alpha[0];
+          o[n][2] *= alpha[1]; o[n][3] *= alpha[1];
+        }
+        pv_tile<NT / 2, WIDE>(o, s2, vs, krow);
+      };
+      if (kparts == 4) part(std::integral_constant<int, 1>{});
+      else part(std::integral_constant<int, 2>{});
       continue;
     }
     float s[BN / 8][4];

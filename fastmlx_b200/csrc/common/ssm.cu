@@ -81,7 +81,7 @@ ssm_prepare_kernel(const T* __restrict__ proj, long long stride, const float* __
 // A token's operands (B and C of the head's group, the block's x values, dt and decay) come through shared memory in
 // runs of TB tokens, the next run copied (cp.async) while the current one is walked.
 template <int NPL, int L, int TB>
-__global__ void __launch_bounds__(128)
+__global__ void __launch_bounds__(128, NPL <= 8 ? 6 : 1)
 ssm_scan_kernel(const float* xbc, const float* dd, const float* __restrict__ d_skip, const int* row_start,
                 const int* row_slot, float* state, long long slot_stride, float* out, int H, int G, int N, int P,
                 int max_slots) {
@@ -106,7 +106,7 @@ ssm_scan_kernel(const float* xbc, const float* dd, const float* __restrict__ d_s
   const bool live = col < P;
   const int colc = live ? col : P - 1;           // lanes beyond the last column follow it and write nothing
   float* sp = state + (long long)slot * slot_stride + ((long long)h * P + colc) * N;
-  float S[NPL], b[NPL], c[NPL];
+  float S[NPL];
   const bool vec = (N & 3) == 0 && (slot_stride & 3) == 0 && (((uintptr_t)state) & 15) == 0;
   if (vec) {
 #pragma unroll
@@ -168,28 +168,76 @@ ssm_scan_kernel(const float* xbc, const float* dd, const float* __restrict__ d_s
     __syncthreads();
     const float* buf = runs + (run & 1) * TB * ROWF;
     const int cnt = min(TB, n - run * TB);
-#pragma unroll 2
-    for (int s = 0; s < cnt; ++s) {
+    // a token's operands out of the run's buffer: this lane's rows of B and C, the column's x, the head's dt and decay
+    struct Operands { float b[NPL], c[NPL], x, dt, decay; };
+    auto fetch = [&](int s, Operands& t) {
       const float* tokp = buf + s * ROWF;
 #pragma unroll
       for (int i = 0; i < NPL; i += 4) {           // 16-byte loads: a run's rows and a lane's share start on 16 bytes
         const float4 b4 = *reinterpret_cast<const float4*>(tokp + sub * NPL + i);
         const float4 c4 = *reinterpret_cast<const float4*>(tokp + NP + sub * NPL + i);
-        b[i] = b4.x; b[i + 1] = b4.y; b[i + 2] = b4.z; b[i + 3] = b4.w;
-        c[i] = c4.x; c[i + 1] = c4.y; c[i + 2] = c4.z; c[i + 3] = c4.w;
+        t.b[i] = b4.x; t.b[i + 1] = b4.y; t.b[i + 2] = b4.z; t.b[i + 3] = b4.w;
+        t.c[i] = c4.x; t.c[i + 1] = c4.y; t.c[i + 2] = c4.z; t.c[i + 3] = c4.w;
       }
-      const float x = tokp[2 * NP + (threadIdx.x / L)], dt = tokp[2 * NP + COLS], decay = tokp[2 * NP + COLS + 1];
-      const float u = dt * x;
+      t.x = tokp[2 * NP + (threadIdx.x / L)];
+      t.dt = tokp[2 * NP + COLS];
+      t.decay = tokp[2 * NP + COLS + 1];
+    };
+    // one token: this lane's rows of the column move on, and it returns its part of the read-out S^T C
+    auto advance = [&](const Operands& t) -> float {
+      const float u = t.dt * t.x;
       float op[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
       for (int i = 0; i < NPL; ++i) {
-        S[i] = fmaf(b[i], u, S[i] * decay);
-        op[i & 3] = fmaf(S[i], c[i], op[i & 3]);
+        S[i] = fmaf(t.b[i], u, S[i] * t.decay);
+        op[i & 3] = fmaf(S[i], t.c[i], op[i & 3]);
       }
-      float o = (op[0] + op[1]) + (op[2] + op[3]);
+      return (op[0] + op[1]) + (op[2] + op[3]);
+    };
+    if (L <= TB && n > 1) {
+     if constexpr (L <= TB) {
+      // L tokens at a time: the lanes' parts of L read-outs are added up across the column's L lanes together, each
+      // round halving what a lane holds (L - 1 exchanges for L tokens, none waiting for another), and lane j is left
+      // with token j's sum, which it writes.  The pairs of lanes that meet in a round are the same for every token,
+      // so a token's sum does not depend on its place in the run.
+      for (int gb = 0; gb < cnt; gb += L) {
+        float v[L];
+        Operands cur, nxt;                         // the next token's operands are on their way while this one is walked
+        fetch(gb, cur);
 #pragma unroll
-      for (int k = 1; k < L; k <<= 1) o += __shfl_xor_sync(0xffffffffu, o, k);
-      if (live && sub == 0) out[(long long)(first + run * TB + s) * inner + (long long)h * P + col] = fmaf(skip, x, o);
+        for (int j = 0; j < L; ++j) {
+          if (j + 1 < L && gb + j + 1 < cnt) fetch(gb + j + 1, nxt);
+          v[j] = gb + j < cnt ? advance(cur) : 0.f;
+          if (j + 1 < L) cur = nxt;
+        }
+#pragma unroll
+        for (int d = L / 2; d >= 1; d >>= 1) {
+          const bool upper = (sub & d) != 0;
+#pragma unroll
+          for (int j = 0; j < d; ++j) {
+            const float give = upper ? v[j] : v[j + d], keep = upper ? v[j + d] : v[j];
+            v[j] = keep + __shfl_xor_sync(0xffffffffu, give, d);
+          }
+        }
+        const int s = gb + sub;
+        if (live && s < cnt) {
+          const float x = buf[s * ROWF + 2 * NP + (threadIdx.x / L)];
+          out[(long long)(first + run * TB + s) * inner + (long long)h * P + col] = fmaf(skip, x, v[0]);
+        }
+      }
+     }
+    } else {
+      // a row of one token (and columns of 32 lanes): every lane gets the sum, by the same pairs in the same order
+#pragma unroll 2
+      for (int s = 0; s < cnt; ++s) {
+        Operands cur;
+        fetch(s, cur);
+        float o = advance(cur);
+#pragma unroll
+        for (int k = L / 2; k >= 1; k >>= 1) o += __shfl_xor_sync(0xffffffffu, o, k);
+        const float x = buf[s * ROWF + 2 * NP + (threadIdx.x / L)];
+        if (live && sub == 0) out[(long long)(first + run * TB + s) * inner + (long long)h * P + col] = fmaf(skip, x, o);
+      }
     }
     __syncthreads();                             // the run is walked: its buffer may take the run after the next
   }

@@ -206,8 +206,17 @@ class LatentAttention(Mixer):
         k, ps = self.rt.k, g.page_size
         T, H, D, R, Dv, r = q.shape[0], self.nh, self.hd, self.rot, self.vd, self.kv_rank
         E = D + R
-        rows_t, blks_t, n = self.pages_in_sight(ctx, g)
-        pages = g.block_tables[rows_t, blks_t].long().clamp_(min=0)
+        # which pages are in sight, and the step's block table over them, serve every layer of the step with this sight
+        # over this cache group (a layer that reads another's cache among them)
+        key = ("pages in sight", id(g), self.window)
+        seen = ctx.scratch.get(key)
+        if seen is None:
+            rows_t, blks_t, n = self.pages_in_sight(ctx, g)
+            pages = g.block_tables[rows_t, blks_t].long().clamp_(min=0)
+            table = torch.full_like(g.block_tables, -1)
+            table[rows_t, blks_t] = torch.arange(n, dtype=torch.int32, device=q.device)
+            seen = ctx.scratch[key] = (pages, n, SimpleNamespace(block_tables=table, page_size=ps, window=self.window))
+        pages, n, group = seen
         cached = cache.kv.view(cache.kv.shape[0], ps, self.row)[pages]           # [pages in sight, page, kv_rank + R]
         kv = k.linear(cached[..., :r].reshape(-1, r), self.ukv, None, torch.bfloat16)       # [n * page, H * (dim + vdim)]
         own = torch.zeros((n, 2, H, ps, E), dtype=torch.bfloat16, device=q.device)
@@ -215,10 +224,6 @@ class LatentAttention(Mixer):
         if R:
             own[:, 0, :, :, D:] = cached[..., r:].unsqueeze(1)
         own[:, 1, :, :, :Dv] = kv[:, H * D:].view(n, ps, H, Dv).permute(0, 2, 1, 3)
-        table = torch.full_like(g.block_tables, -1)
-        table[rows_t, blks_t] = torch.arange(n, dtype=torch.int32, device=q.device)
-        group = SimpleNamespace(block_tables=table, page_size=ps, window=self.window)
-        ctx.scratch.setdefault("pages of a step", []).append(group)       # kept for the step: its identity keys cached views
         q_wide.view(T, H, E)[..., :D] = q.view(T, H, E)[..., :D]
         opts = dict(sinks=self.sinks) if self.sinks is not None else {}
         out = k.paged_attention_wide(q_wide, own, ctx, group, H, H, E, self.scale, 0.0, self.window, **opts)
