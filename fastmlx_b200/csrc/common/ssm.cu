@@ -81,7 +81,7 @@ ssm_prepare_kernel(const T* __restrict__ proj, long long stride, const float* __
 // A token's operands (B and C of the head's group, the block's x values, dt and decay) come through shared memory in
 // runs of TB tokens, the next run copied (cp.async) while the current one is walked.
 template <int NPL, int L, int TB>
-__global__ void __launch_bounds__(128, NPL <= 8 ? 6 : 1)
+__global__ void __launch_bounds__(128)
 ssm_scan_kernel(const float* xbc, const float* dd, const float* __restrict__ d_skip, const int* row_start,
                 const int* row_slot, float* state, long long slot_stride, float* out, int H, int G, int N, int P,
                 int max_slots) {
