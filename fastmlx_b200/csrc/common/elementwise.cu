@@ -3,6 +3,28 @@
 #include <math.h>
 #include "common.cuh"
 
+// out[t, :] = table[ids[t], :] * scale in 32-bit: an embedding that is multiplied by a constant and starts the
+// 32-bit stream.  A bad id leaves a status code and a row of zeros.
+template <typename T>
+__global__ void embed_scaled_kernel(const T* table, const int* ids, float* out, int d, long long nrows, float scale,
+                                    int* status, int code) {
+  pdl_wait();
+  pdl_trigger();
+  const int t = blockIdx.x;
+  const long long id = ids[t];
+  float* dst = out + (long long)t * d;
+  if (id < 0 || id >= nrows) {
+    if (threadIdx.x == 0) fmx_set_status(status, code, id, t);
+    for (int i = threadIdx.x; i < d; i += blockDim.x) dst[i] = 0.f;
+    return;
+  }
+  const T* src = table + id * d;
+  for (int i = threadIdx.x; i < d; i += blockDim.x) dst[i] = to_f(src[i]) * scale;
+}
+
+FMX_EXPORT int fmx_embed_scaled(const void* table, int dtype, const int* ids, float* out, int n, int d, long long nrows,
+                                float scale, int* status, int code, cudaStream_t stream);
+
 // out[t, :] = table[ids[t], :].  A bad id leaves a status code and a row of zeros.
 template <typename T>
 __global__ void gather_rows_kernel(const T* table, const int* ids, T* out,
@@ -387,6 +409,22 @@ FMX_EXPORT int fmx_activation(const void* x, long long x_stride, void* out, long
                (long long)rows, cols, kind);
   else
     return fmx_fail("fmx_activation: unknown dtype %d", dtype);
+  FMX_LAUNCH_CHECK();
+  return 0;
+}
+
+// The scaled embedding: rows of a table of type `dtype`, times `scale`, out in 32-bit.
+FMX_EXPORT int fmx_embed_scaled(const void* table, int dtype, const int* ids, float* out, int n, int d, long long nrows,
+                                float scale, int* status, int code, cudaStream_t stream) {
+  if (n == 0) return 0;
+  if (n < 0 || d <= 0 || nrows <= 0) return fmx_fail("fmx_embed_scaled: bad sizes n=%d d=%d rows=%lld", n, d, nrows);
+  const int block = d >= 1024 ? 256 : 128;
+  if (dtype == FMX_F32)
+    fmx_launch(embed_scaled_kernel<float>, dim3(n), dim3(block), 0, stream, (const float*)table, ids, out, d, nrows, scale, status, code);
+  else if (dtype == FMX_BF16)
+    fmx_launch(embed_scaled_kernel<bf16>, dim3(n), dim3(block), 0, stream, (const bf16*)table, ids, out, d, nrows, scale, status, code);
+  else
+    return fmx_fail("fmx_embed_scaled: unknown dtype %d", dtype);
   FMX_LAUNCH_CHECK();
   return 0;
 }

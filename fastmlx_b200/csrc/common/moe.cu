@@ -28,7 +28,7 @@ __device__ __forceinline__ void warp_argmax(float& v, int& i) {
 
 __global__ void __launch_bounds__(ROUTE_WARPS * 32)
 moe_route_kernel(const float* z, long long z_stride, int T, int E, int top, int groups, int keep, float* weights,
-                 int* chosen) {
+                 int* chosen, const float* __restrict__ choice_bias, float weight_scale) {
   extern __shared__ float smem[];               // per warp: E scores, E marks (as floats), `groups` group scores
   pdl_wait();
   pdl_trigger();
@@ -78,10 +78,12 @@ moe_route_kernel(const float* z, long long z_stride, int T, int E, int top, int 
     }
   }
   for (int k = 0; k < top; ++k) {
-    float bv = -2.f;
+    float bv = -INFINITY;
     int bi = 0x7fffffff;
-    for (int e = lane; e < E; e += 32)
-      if (ok[e] != 0.f && s[e] > bv) { bv = s[e]; bi = e; }
+    for (int e = lane; e < E; e += 32) {
+      const float cv = s[e] + (choice_bias != nullptr ? choice_bias[e] : 0.f);    // chosen by score + bias, weighed by score
+      if (ok[e] != 0.f && (cv > bv || bi == 0x7fffffff)) { bv = cv; bi = e; }
+    }
     warp_argmax(bv, bi);
     if (bi >= E) {                               // fewer allowed experts than `top`
       if (lane == 0 && chosen != nullptr) chosen[(long long)t * top + k] = -1;
@@ -89,7 +91,7 @@ moe_route_kernel(const float* z, long long z_stride, int T, int E, int top, int 
     }
     if (lane == 0) {
       ok[bi] = 0.f;
-      weights[(long long)t * E + bi] = s[bi];
+      weights[(long long)t * E + bi] = s[bi] * weight_scale;
       if (chosen != nullptr) chosen[(long long)t * top + k] = bi;
     }
     __syncwarp();
@@ -156,15 +158,25 @@ __global__ void moe_expert_act_vec_kernel(const bf16* gu, long long gu_stride, c
 }
 }  // namespace
 
+// choice_bias ([E], may be null): added to the scores for the choice only; weight_scale multiplies the chosen scores.
+FMX_EXPORT int fmx_moe_route_biased(const float* z, long long z_stride, int T, int E, int top, int groups, int keep,
+                                    float* weights, int* chosen, const float* choice_bias, float weight_scale,
+                                    cudaStream_t stream);
 FMX_EXPORT int fmx_moe_route(const float* z, long long z_stride, int T, int E, int top, int groups, int keep, float* weights,
                              int* chosen, cudaStream_t stream) {
+  return fmx_moe_route_biased(z, z_stride, T, E, top, groups, keep, weights, chosen, nullptr, 1.0f, stream);
+}
+
+FMX_EXPORT int fmx_moe_route_biased(const float* z, long long z_stride, int T, int E, int top, int groups, int keep,
+                                    float* weights, int* chosen, const float* choice_bias, float weight_scale,
+                                    cudaStream_t stream) {
   if (T == 0) return 0;
   if (T < 0 || E <= 0 || top <= 0 || top > E || groups <= 0 || E % groups || keep <= 0 || z_stride < E)
     return fmx_fail("fmx_moe_route: bad sizes T=%d E=%d top=%d groups=%d keep=%d", T, E, top, groups, keep);
   const size_t smem = (size_t)ROUTE_WARPS * (2 * (size_t)E + groups) * sizeof(float);
   if (smem > 48 * 1024) return fmx_fail("fmx_moe_route: %d experts are more than the kernel's shared memory holds", E);
   fmx_launch(moe_route_kernel, dim3((T + ROUTE_WARPS - 1) / ROUTE_WARPS), dim3(ROUTE_WARPS * 32), smem, stream, z, z_stride, T, E,
-             top, groups, keep, weights, chosen);
+             top, groups, keep, weights, chosen, choice_bias, weight_scale);
   FMX_LAUNCH_CHECK();
   return 0;
 }

@@ -7,11 +7,36 @@
 //
 // sigmoid_gate: o[t, j] *= sigmoid(g[t, j / group]) in 32-bit: group = 1 gates element by element, group = the
 // head's width gates a head by one value.
+//
+// rmsnorm_pair_mean: out = (a / rms(a) * wa + b / rms(b) * wb) / 2, each row of a and of b divided by its own root mean
+// square: how a layer joins two mixers that ran side by side on the same input.
 #include <math.h>
 #include "common.cuh"
 
 namespace {
 constexpr int NORM_BLOCK = 128;
+
+template <typename TI, typename TO>
+__global__ void __launch_bounds__(NORM_BLOCK)
+rmsnorm_pair_mean_kernel(const TI* a, long long a_stride, const TI* b, long long b_stride, const float* __restrict__ wa,
+                         const float* __restrict__ wb, float eps, TO* out, long long out_stride, int n) {
+  pdl_wait();
+  pdl_trigger();
+  const long long t = blockIdx.x;
+  const TI* pa = a + t * a_stride;
+  const TI* pb = b + t * b_stride;
+  float sa = 0.f, sb = 0.f;
+  for (int e = threadIdx.x; e < n; e += NORM_BLOCK) {
+    const float x = to_f(pa[e]), y = to_f(pb[e]);
+    sa = fmaf(x, x, sa);
+    sb = fmaf(y, y, sb);
+  }
+  const float ma = 1.0f / sqrtf(block_sum<NORM_BLOCK>(sa) / (float)n + eps);
+  const float mb = 1.0f / sqrtf(block_sum<NORM_BLOCK>(sb) / (float)n + eps);
+  TO* dst = out + t * out_stride;
+  for (int e = threadIdx.x; e < n; e += NORM_BLOCK)
+    dst[e] = from_f<TO>(0.5f * (to_f(pa[e]) * ma * wa[e] + to_f(pb[e]) * mb * wb[e]));
+}
 
 template <typename TI, typename TO>
 __global__ void __launch_bounds__(NORM_BLOCK)
@@ -125,6 +150,26 @@ FMX_EXPORT int fmx_sigmoid_gate(void* o, long long o_stride, int o_dtype, const 
   else if (o_dtype == FMX_BF16 && g_dtype == FMX_BF16) FMX_SG(bf16, bf16);
   else return fmx_fail("fmx_sigmoid_gate: unknown dtypes %d, %d", o_dtype, g_dtype);
 #undef FMX_SG
+  FMX_LAUNCH_CHECK();
+  return 0;
+}
+
+// a and b: rows of n values of type in_dtype; out of type out_dtype.
+FMX_EXPORT int fmx_rmsnorm_pair_mean(const void* a, long long a_stride, const void* b, long long b_stride, int in_dtype,
+                                     const float* wa, const float* wb, float eps, void* out, long long out_stride, int out_dtype,
+                                     int rows, int n, cudaStream_t stream) {
+  if (rows == 0) return 0;
+  if (rows < 0 || n <= 0 || a_stride < n || b_stride < n || out_stride < n)
+    return fmx_fail("fmx_rmsnorm_pair_mean: bad sizes rows=%d n=%d", rows, n);
+#define FMX_PM(TI, TO)                                                                                                   \
+  fmx_launch(rmsnorm_pair_mean_kernel<TI, TO>, dim3(rows), dim3(NORM_BLOCK), 0, stream, (const TI*)a, a_stride, (const TI*)b, \
+             b_stride, wa, wb, eps, (TO*)out, out_stride, n)
+  if (in_dtype == FMX_F32 && out_dtype == FMX_F32) FMX_PM(float, float);
+  else if (in_dtype == FMX_F32 && out_dtype == FMX_BF16) FMX_PM(float, bf16);
+  else if (in_dtype == FMX_BF16 && out_dtype == FMX_BF16) FMX_PM(bf16, bf16);
+  else if (in_dtype == FMX_BF16 && out_dtype == FMX_F32) FMX_PM(bf16, float);
+  else return fmx_fail("fmx_rmsnorm_pair_mean: unknown dtypes %d, %d", in_dtype, out_dtype);
+#undef FMX_PM
   FMX_LAUNCH_CHECK();
   return 0;
 }

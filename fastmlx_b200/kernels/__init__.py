@@ -651,6 +651,84 @@ def gated_group_rmsnorm(y, z, weight, eps, groups, out_dtype, out=None) -> torch
     return out
 
 
+# ----------------------------------------------------------------------------- scaled embedding, retention, sigmoid attention
+def embed_scaled(ids, table, scale: float, status) -> torch.Tensor:
+    """table[id_t] * scale in 32-bit, [T, d]: an embedding that starts the 32-bit stream."""
+    _need_cuda(table, ids)
+    assert ids.dtype == torch.int32 and table.dim() == 2 and table.is_contiguous()
+    n, d = ids.numel(), table.shape[1]
+    out = torch.empty((n, d), dtype=torch.float32, device=table.device)
+    call("common", "fmx_embed_scaled", table.data_ptr(), _dt(table), ids.data_ptr(), out.data_ptr(), n, d, table.shape[0],
+         float(scale), _ptr(status), BAD_TOKEN, _stream())
+    return out
+
+
+def rmsnorm_pair_mean(a, b, wa, wb, eps: float, out_dtype) -> torch.Tensor:
+    """(a / rms(a) * wa + b / rms(b) * wb) / 2, row by row, in 32-bit; rows of a and b may be slices."""
+    _need_cuda(a, b, wa, wb)
+    assert a.dim() == 2 and a.shape == b.shape and a.dtype == b.dtype and a.stride(1) == 1 and b.stride(1) == 1
+    assert wa.dtype == torch.float32 and wb.dtype == torch.float32 and wa.numel() == a.shape[1] == wb.numel()
+    T, n = a.shape
+    out = torch.empty((T, n), dtype=out_dtype, device=a.device)
+    call("common", "fmx_rmsnorm_pair_mean", a.data_ptr(), a.stride(0), b.data_ptr(), b.stride(0), _dt(a), wa.data_ptr(),
+         wb.data_ptr(), float(eps), out.data_ptr(), out.stride(0), _dt(out), T, n, _stream())
+    return out
+
+
+def retention_prepare(proj, positions, inv_freq, decay, H: int, D: int, P: int, rot: int, k_scale: float):
+    """What a retention's recurrence takes in, from a step's projection proj[T, q (H*D) | k (H*D) | v (H*P) ...] (rows may be
+    a slice): q and k rotated over their first `rot` dimensions (half-split pairing), k times `k_scale` after the
+    rotation.  -> (v | k | q in 32-bit [T, H*P + 2*H*D], the layout `ssm_scan` reads as x | B | C with as many groups as
+    heads; step size 1 | decay per head in 32-bit [T, 2H])."""
+    _need_cuda(proj, positions, inv_freq, decay)
+    assert proj.dim() == 2 and proj.stride(1) == 1 and positions.dtype == torch.int32
+    assert decay.dtype == torch.float32 and decay.numel() == H
+    T = proj.shape[0]
+    xbc = torch.empty((T, H * P + 2 * H * D), dtype=torch.float32, device=proj.device)
+    dd = torch.empty((T, 2 * H), dtype=torch.float32, device=proj.device)
+    call("common", "fmx_retention_prepare", proj.data_ptr(), proj.stride(0), _dt(proj), positions.data_ptr(), _ptr(inv_freq),
+         decay.data_ptr(), xbc.data_ptr(), dd.data_ptr(), T, int(H), int(D), int(P), int(rot), float(k_scale), _stream())
+    return xbc, dd
+
+
+def retention_gate_norm(o, gate, eps: float, H: int, P: int, out_dtype, out=None) -> torch.Tensor:
+    """o[T, H*P] (32-bit) per head divided by its root mean square (no weight), times silu(gate); gate (of its own type)
+    and out may be slices of wider buffers."""
+    _need_cuda(o, gate, out)
+    T = o.shape[0]
+    if out is None:
+        out = torch.empty((T, H * P), dtype=out_dtype, device=o.device)
+    assert o.is_contiguous() and o.dtype == torch.float32 and gate.stride(1) == 1 and out.stride(1) == 1
+    assert gate.shape == (T, H * P) and out.shape == (T, H * P)
+    call("common", "fmx_retention_gate_norm", o.data_ptr(), gate.data_ptr(), gate.stride(0), _dt(gate), out.data_ptr(),
+         out.stride(0), _dt(out), T, int(H), int(P), float(eps), _stream())
+    return out
+
+
+def sigmoid_attention(q, kv, ctx, group, nh, nkv, hd, vd, scale, softcap, window, page_size, head_bias, mix, out=None,
+                      out_dtype=None) -> torch.Tensor:
+    """Attention without a softmax: a visible key weighs sigmoid(cap(scale q.k) + head_bias[head]); the heads' weights are
+    mixed by `mix` ([nh, nh], 32-bit: row h lists what head h takes of every head's weights) and head h applies its mixed
+    weights to the values of its own key/value head.  Queries q[T, nh*hd] of their own type over pages of [nkv, page, hd]
+    keys and [nkv, page, vd] values; scores, weights and the sums over keys are 32-bit.  -> [T, nh*vd]."""
+    _need_cuda(q, kv, head_bias, mix, out)
+    assert kv.is_contiguous() and q.stride(1) == 1
+    T = q.shape[0]
+    if out is None:
+        out = torch.empty((T, nh * vd), dtype=out_dtype or kv.dtype, device=q.device)
+    assert out.stride(1) == 1 and out.shape == (T, nh * vd)
+    assert mix.dtype == torch.float32 and mix.is_contiguous() and mix.shape == (nh, nh)
+    assert head_bias is None or (head_bias.dtype == torch.float32 and head_bias.numel() == nh)
+    bt = group.block_tables
+    part = torch.empty((T, nh, nkv, vd), dtype=torch.float32, device=q.device)
+    call("common", "fmx_sigmoid_attention", q.data_ptr(), q.stride(0), _dt(q), kv.data_ptr(), bt.data_ptr(), bt.stride(0),
+         ctx.token_row.data_ptr(), ctx.positions.data_ptr(), part.data_ptr(), T, nh, nkv, hd, vd, int(page_size), kv.shape[0],
+         float(scale), float(softcap or 0.0), int(window), bt.shape[0], _dt(kv), _ptr(head_bias), _ptr(ctx.status), _stream())
+    call("common", "fmx_head_mix", part.data_ptr(), mix.data_ptr(), out.data_ptr(), out.stride(0), _dt(out), T, nh, nkv, vd,
+         _stream())
+    return out
+
+
 # ----------------------------------------------------------------------------- dynamic tanh, latents, gates, routed experts
 def dyt_step(y, post, mult, add, residual, pre, out_dtype, out=None, keep_stream: bool = True):
     """One pass over the stream: residual <- residual + mult * post(y) + add, out = pre(residual), all 32-bit.
@@ -706,18 +784,39 @@ def sigmoid_gate(o, gate, group: int = 1):
     return o
 
 
-def moe_route(logits, top: int, groups: int = 1, keep: int = 1, want_chosen: bool = False):
+def moe_route(logits, top: int, groups: int = 1, keep: int = 1, want_chosen: bool = False, experts: int | None = None,
+              correction=None, scale: float = 1.0):
     """Router logits [T, E] (32-bit) -> weights [T, E] (32-bit): the softmax score where an expert is among the token's
     `top` best of the `keep` best groups (of `groups` groups of neighbours, each scored by its best member), else zero;
-    not renormalised.  With `want_chosen` also the chosen indices, int32 [T, top]."""
-    _need_cuda(logits)
+    not renormalised.  With `want_chosen` also the chosen indices, int32 [T, top].  `experts`: the row's first that many
+    columns are the experts' logits (a row may hold other columns behind them).  `correction` (32-bit [E]): added to the
+    scores for the choice only; `scale` multiplies the chosen experts' scores."""
+    _need_cuda(logits, correction)
     assert logits.dim() == 2 and logits.dtype == torch.float32 and logits.stride(1) == 1
-    T, E = logits.shape
+    T, E = logits.shape[0], int(experts if experts is not None else logits.shape[1])
+    assert E <= logits.shape[1] and (correction is None or (correction.dtype == torch.float32 and correction.numel() == E
+                                                             and correction.is_contiguous()))
     w = torch.empty((T, E), dtype=torch.float32, device=logits.device)
     chosen = torch.empty((T, top), dtype=torch.int32, device=logits.device) if want_chosen else None
-    call("common", "fmx_moe_route", logits.data_ptr(), logits.stride(0), T, E, int(top), int(groups), int(keep), w.data_ptr(),
-         _ptr(chosen), _stream())
+    call("common", "fmx_moe_route_biased", logits.data_ptr(), logits.stride(0), T, E, int(top), int(groups), int(keep),
+         w.data_ptr(), _ptr(chosen), _ptr(correction), float(scale), _stream())
     return (w, chosen) if want_chosen else w
+
+
+def moe_plain_act(u, weights, E: int, ff: int, act: str, shared_gate=None, out=None):
+    """The hidden layers of experts without a gate, side by side: u[T, F], F = E*ff + the shared expert's width;
+    -> [T, F]: w * act(u) with w the token's weight for the column's expert, zero where it did not choose it; the shared
+    columns at the end weigh sigmoid(shared_gate[t]) (32-bit, one value per token; rows may be a slice) or 1."""
+    _need_cuda(u, weights, shared_gate)
+    assert u.dim() == 2 and u.stride(1) == 1 and weights.dtype == torch.float32 and weights.is_contiguous()
+    T, F = u.shape
+    assert weights.shape == (T, E) and (shared_gate is None or (shared_gate.dtype == torch.float32 and shared_gate.shape[0] == T))
+    if out is None:
+        out = torch.empty((T, F), dtype=u.dtype, device=u.device)
+    call("common", "fmx_moe_plain_act", u.data_ptr(), u.stride(0), weights.data_ptr(), _ptr(shared_gate),
+         shared_gate.stride(0) if shared_gate is not None else 0, out.data_ptr(), out.stride(0), T, int(E), int(ff), F,
+         ACTIVATIONS[act], _dt(u), _stream())
+    return out
 
 
 def moe_expert_act(gu, weights, E: int, ff: int, limit: float, limit_shared: float = 0.0, out=None, block: int = 0):

@@ -59,6 +59,14 @@ _SIGNATURES = {
         "fmx_ssm_scan": [_P, _P, _P, _P, _P, _P, _L, _P, _I, _I, _I, _I, _I, _I, _I, _P],
         "fmx_gated_group_rmsnorm": [_P, _P, _L, _P, _P, _L, _I, _I, _I, _F, _I, _P],
         "fmx_act_mul": [_P, _P, _I, _I, _I, _I, _I, _P],
+        "fmx_embed_scaled": [_P, _I, _P, _P, _I, _I, _L, _F, _P, _I, _P],
+        "fmx_rmsnorm_pair_mean": [_P, _L, _P, _L, _I, _P, _P, _F, _P, _L, _I, _I, _I, _P],
+        "fmx_moe_route_biased": [_P, _L, _I, _I, _I, _I, _I, _P, _P, _P, _F, _P],
+        "fmx_moe_plain_act": [_P, _L, _P, _P, _L, _P, _L, _I, _I, _I, _I, _I, _I, _P],
+        "fmx_retention_prepare": [_P, _L, _I, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _F, _P],
+        "fmx_retention_gate_norm": [_P, _P, _L, _I, _P, _L, _I, _I, _I, _I, _F, _P],
+        "fmx_sigmoid_attention": [_P, _L, _I, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _L, _F, _F, _I, _I, _I, _P, _P, _P],
+        "fmx_head_mix": [_P, _P, _P, _L, _I, _I, _I, _I, _I, _P],
     },
     "bf16": {
         "fmx_gemv": [_P, _L, _P, _L, _P, _P, _L, _P, _L, _I, _I, _I, _I, _I, _I, _I, _P],

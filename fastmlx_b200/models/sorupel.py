@@ -15,21 +15,8 @@ from __future__ import annotations
 
 from .. import registry
 from ..config.sorupel import SorupelConfig
-from ..parts import (BigramEmbedding, Embedding, GQAAttention, LatentAttention, LMHead, Model, NoPositionEncoding,
+from ..parts import (BigramEmbedding, Embedding, GQAAttention, LatentAttention, LMHead, MixerOnly, Model, NoPositionEncoding,
                      PreNormBlock, RMSNorm, RotaryEmbedding, Run, StateSpaceMixer, SwiGLU)
-
-
-class MixerOnly(PreNormBlock):
-    """A pre-norm layer without a feed-forward: x <- x + mixer(norm1(x))."""
-
-    def __init__(self, mixer, norm1):
-        self.mixer, self.ffn, self.norm1, self.norm2 = mixer, None, norm1, None
-
-    def children(self):
-        return (self.norm1, self.mixer)
-
-    def forward(self, delta, residual, ctx, cache):
-        return self.mixer.forward_in_block(delta, residual, self.norm1, ctx, cache)
 
 
 def build_sorupel(cfg: SorupelConfig) -> Model:

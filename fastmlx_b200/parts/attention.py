@@ -41,6 +41,11 @@ class GQAAttention(Mixer):
     runs counted from position 0 of the request whatever the cut of its prompt; the cache gives earlier runs' pages
     back.  `sink` s: the softmax's denominator has one more term exp(s) that has no value (s = 0 adds one).
     `gate_per_head`: the gate has one value per head, not one per output element.
+
+    And a form without a softmax.  `weights="sigmoid"`: a visible key weighs sigmoid(score + b_h) with one number per
+    head (`head_bias`: its tensor's name, or None for no number); nothing is normalised over the keys.  `head_mix` (a
+    tensor's name, [heads, heads]): the heads' weights are mixed, w'_h = sum_g M[h, g] w_g, before head h applies them to
+    the values of its own key/value head.  Scores, weights and their sums over the keys are 32-bit.
     """
 
     supports_cuda_graph = True
@@ -53,7 +58,8 @@ class GQAAttention(Mixer):
                  weight_suffix: str = ".weight", bias_suffix: str = ".bias", qk_norm_weights=None,
                  qk_norm_first: bool = False, keep_first: int = 0, gate: str | None = None, late_bias: bool = False,
                  out_bias: bool | None = None, values_from_keys: bool = False, qk_norm_whole: bool = False,
-                 chunk: int = 0, sink: float | None = None, gate_per_head: bool = False):
+                 chunk: int = 0, sink: float | None = None, gate_per_head: bool = False, weights: str = "softmax",
+                 head_bias: str | None = None, head_mix: str | None = None):
         if num_heads % num_kv_heads:
             raise ValueError(f"{num_heads} query heads are no multiple of {num_kv_heads} kv heads")
         self.nh, self.nkv, self.hd = int(num_heads), int(num_kv_heads), int(head_dim)
@@ -66,6 +72,16 @@ class GQAAttention(Mixer):
         self.late_bias = bool(late_bias) and bool(bias)
         self.values_from_keys, self.qk_norm_whole = bool(values_from_keys), bool(qk_norm_whole)
         self.chunk, self.sink, self.gate_per_head = int(chunk or 0), None if sink is None else float(sink), bool(gate_per_head)
+        if weights not in ("softmax", "sigmoid"):
+            raise ValueError(f"attention weights are a softmax or sigmoids, not {weights!r}")
+        self.sigmoid = weights == "sigmoid"
+        self.head_bias_name = f"{name}.{head_bias}" if head_bias else None
+        self.head_mix_name = f"{name}.{head_mix}" if head_mix else None
+        if not self.sigmoid and (head_bias or head_mix):
+            raise ValueError("a number per head and a mix of the heads' weights belong to sigmoid weights")
+        if self.sigmoid and (chunk or sink is not None or gate or keep_first or share_kv):
+            raise ValueError("sigmoid weights come without runs of positions, extra terms, gates, kept tokens or a shared cache")
+        self.head_bias = self.head_mix = None
         if self.chunk and window:
             raise ValueError("a layer masks by a window or by runs of positions, not both")
         if self.values_from_keys and (self.vd != self.hd or share_kv):
@@ -79,7 +95,7 @@ class GQAAttention(Mixer):
             raise ValueError("a weight or an order for the q/k norm needs its eps")
         self.general = (self.softcap > 0 or self.qk_norm_eps is not None or self.vd != self.hd or self.keep_first > 0
                         or self.gate_name is not None or self.late_bias or self.values_from_keys or self.chunk > 0
-                        or self.sink is not None)
+                        or self.sink is not None or self.sigmoid)
         self.scale = float(scale) if scale is not None else float(head_dim) ** -0.5
         self.window = int(window)
         self.share_kv = bool(share_kv)
@@ -108,6 +124,10 @@ class GQAAttention(Mixer):
         if self.qk_norm_weights:
             widths = (self.nh * self.hd, self.nkv * self.hd) if self.qk_norm_whole else (self.hd, self.hd)
             specs += [WeightSpec(n, (w,), "norm") for n, w in zip(self.qk_norm_weights, widths)]
+        if self.head_mix_name:
+            specs.append(WeightSpec(self.head_mix_name, (self.nh, self.nh), "head_mix"))
+        if self.head_bias_name:
+            specs.append(WeightSpec(self.head_bias_name, (self.nh,), "head_bias"))
         return specs
 
     def bind_own(self, tensors, rt: Runtime):
@@ -117,6 +137,10 @@ class GQAAttention(Mixer):
             self.q_weight, self.k_weight = (to_f32_vector(tensors[n], rt) for n in self.qk_norm_weights)
         if self.sink is not None:
             self.sinks = torch.full((self.nh,), self.sink, dtype=torch.float32, device=rt.device)
+        if self.sigmoid:
+            self.head_mix = to_f32_vector(tensors[self.head_mix_name], rt) if self.head_mix_name else \
+                torch.eye(self.nh, dtype=torch.float32, device=rt.device)
+            self.head_bias = to_f32_vector(tensors[self.head_bias_name], rt) if self.head_bias_name else None
 
     def weight_bytes(self):
         return super().weight_bytes() + 4 * (len(self.bias_names) and self.qkv_features)
@@ -128,11 +152,13 @@ class GQAAttention(Mixer):
     def forward(self, x, ctx, cache):
         return self.o.forward(self.forward_inner(x, ctx, cache))
 
-    def forward_inner(self, x, ctx, cache, out=None):
+    def forward_inner(self, x, ctx, cache, out=None, qkv=None):
         """The heads' outputs side by side, [T, nh * v width], before the output projection; into
-        `out` (a slice of a wider buffer) where one is given."""
+        `out` (a slice of a wider buffer) where one is given.  `qkv`: the part's projection where the caller has
+        computed it already (as a slice of a product that it shares with another part)."""
         extended = self.late_bias or self.gate_name is not None
-        qkv = self.qkv.forward(x, out_dtype=torch.float32 if extended else None)
+        if qkv is None:
+            qkv = self.qkv.forward(x, out_dtype=torch.float32 if extended or self.sigmoid else None)
         if not self.general:
             res = self._attend(qkv, ctx, cache)
             if out is None:
@@ -150,6 +176,9 @@ class GQAAttention(Mixer):
                                  norm_first=self.qk_norm_first) if extended or self.q_weight is not None or self.qk_norm_first
                             else {}), **more)
         gate = qkv[:, self.qkv_features:] if self.gate_name else None
+        if self.sigmoid:
+            return k.sigmoid_attention(q, cache.kv, ctx, g, self.nh, self.nkv, self.hd, self.vd, self.scale, self.softcap,
+                                       self.window, g.page_size, self.head_bias, self.head_mix, out=out, out_dtype=self.rt.dtype)
         if self.chunk or self.sinks is not None or self.gate_per_head:
             # runs of positions, a term without a value in the denominator, one gate value per head
             opts = dict(chunk=self.chunk, sinks=self.sinks, gate=gate, gate_group=self.vd if self.gate_per_head else 1)

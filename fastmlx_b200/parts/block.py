@@ -3,8 +3,8 @@ from __future__ import annotations
 
 import torch
 
-from .base import FeedForward, Mixer, Norm, Part
-from .linear import JoinedLinear
+from .base import FeedForward, Mixer, Norm, Part, WeightSpec, to_f32_vector
+from .linear import JoinedLinear, Linear
 from .norm import Pending
 
 
@@ -43,6 +43,19 @@ class PreNormBlock(Part):
         z = self.ffn.emit(b, x)
         b.release(x)
         return z, stream
+
+
+class MixerOnly(PreNormBlock):
+    """A pre-norm layer without a feed-forward: x <- x + mixer(norm1(x))."""
+
+    def __init__(self, mixer, norm1):
+        self.mixer, self.ffn, self.norm1, self.norm2 = mixer, None, norm1, None
+
+    def children(self):
+        return (self.norm1, self.mixer)
+
+    def forward(self, delta, residual, ctx, cache):
+        return self.mixer.forward_in_block(delta, residual, self.norm1, ctx, cache)
 
 
 class ParallelBlock(Part):
@@ -121,3 +134,58 @@ class SandwichBlock(Part):
             return pending, residual
         h, residual = self.norm2.forward(pending, residual)
         return Pending(self.ffn.forward(h, ctx), self.norm2b, self.mult), residual
+
+
+class PairMixer(Mixer):
+    """Two mixers side by side on the same input: mixer(x) = (N_l(left(x)) + N_r(right(x))) / 2, each branch's output
+    divided by its root mean square over the model width and multiplied by a plain weight of its own (`norm_names`:
+    the two tensors, under `name`) before the two are averaged, in 32-bit.
+
+    The branches' input projections run as one product over x (their matrices are stacked at bind time and each
+    branch is handed its slice, in 32-bit); either branch may keep pages and either a state slot, which the layer's
+    cache entry holds together.  A branch offers `forward_inner(x, ctx, cache, <projection>=slice)` and an output
+    projection `o`; `left` takes its slice as `qkv` (a `GQAAttention`), `right` as `proj` (a `RetentionMixer`)."""
+
+    def __init__(self, width: int, left: Mixer, right: Mixer, norm_eps: float, name: str,
+                 norm_names=("left.out", "right.out"), weight_suffix: str = ""):
+        self.width, self.left, self.right, self.eps = int(width), left, right, float(norm_eps)
+        self.norm_tensors = tuple(f"{name}.{n}" for n in norm_names)
+        if left.cache_spec() is not None and right.cache_spec() is not None:
+            raise ValueError("at most one branch keeps pages")
+        if left.state_spec() is not None and right.state_spec() is not None:
+            raise ValueError("at most one branch keeps a state slot")
+        # one product for both branches' projections; the branches give theirs up
+        self.split = left.qkv.out_features
+        self.proj = Linear(width, list(left.qkv.names) + list(right.proj.names), weight_suffix=weight_suffix)
+        left.qkv = right.proj = None
+        self.w_left = self.w_right = None
+
+    @property
+    def supports_cuda_graph(self):
+        return bool(getattr(self.left, "supports_cuda_graph", False)) and bool(getattr(self.right, "supports_cuda_graph", False))
+
+    def children(self):
+        return (self.proj, self.left, self.right)
+
+    def own_weight_specs(self):
+        return [WeightSpec(n, (self.width,), "norm") for n in self.norm_tensors]
+
+    def bind_own(self, tensors, rt):
+        self.w_left, self.w_right = (to_f32_vector(tensors[n], rt) for n in self.norm_tensors)
+
+    def weight_bytes(self):
+        return super().weight_bytes() + 8 * self.width
+
+    def cache_spec(self):
+        return self.left.cache_spec() or self.right.cache_spec()
+
+    def state_spec(self):
+        return self.left.state_spec() or self.right.state_spec()
+
+    def forward(self, x, ctx, cache):
+        proj = self.proj.forward(x, out_dtype=torch.float32)
+        a = self.left.forward_inner(x, ctx, cache, qkv=proj[:, :self.split])
+        b = self.right.forward_inner(x, ctx, cache, proj=proj[:, self.split:])
+        a = self.left.o.forward(a, out_dtype=torch.float32)
+        b = self.right.o.forward(b, out_dtype=torch.float32)
+        return self.rt.k.rmsnorm_pair_mean(a, b, self.w_left, self.w_right, self.eps, self.rt.dtype)

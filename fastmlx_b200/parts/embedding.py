@@ -7,11 +7,17 @@ from .base import Part, Runtime, StateSpec, WeightSpec, to_compute
 
 
 class Embedding(Part):
-    """h[t] = E[id_t], no scaling (tamnd/fastmlx compute/models/llama.go:385-390)."""
+    """h[t] = E[id_t], no scaling (tamnd/fastmlx compute/models/llama.go:385-390); or, with `scale` s != 1,
+    h[t] = s E[id_t], multiplied in 32-bit: the product is then the 32-bit stream's first value (`starts_stream`)."""
 
-    def __init__(self, vocab: int, width: int, name: str, suffix: str = ".weight"):
+    starts_stream = False
+
+    def __init__(self, vocab: int, width: int, name: str, suffix: str = ".weight", scale: float = 1.0):
         self.vocab, self.width, self.name = int(vocab), int(width), name
         self.tensor = name + suffix
+        self.scale = float(scale)
+        if self.scale != 1.0:
+            self.starts_stream = True
         self.weight = None
 
     def own_weight_specs(self):
@@ -29,13 +35,17 @@ class Embedding(Part):
         return None
 
     def forward(self, ids, ctx, cache=None):
+        if self.scale != 1.0:
+            return self.rt.k.embed_scaled(ids, self.weight, self.scale, ctx.status)
         if self.weight.dtype != self.rt.dtype:          # a table stored in 32-bit under bfloat16 activations
             return self.rt.k.embedding(ids, self.weight, ctx.status, self.rt.dtype)
         return self.rt.k.embedding(ids, self.weight, ctx.status)
 
 
     def emit(self, b) -> int:
-        from ..engine.native import OP_EMBED, _dt
+        from ..engine.native import NotNative, OP_EMBED, _dt
+        if self.scale != 1.0:
+            raise NotNative("a scaled embedding runs in Python only")
         out = b.reg(self.width)
         b.op(OP_EMBED, out0=out, w=b.ptr(self.weight), w_dtype=_dt(self.weight.dtype), n=self.width, table_rows=self.vocab)
         return out

@@ -3,7 +3,7 @@ from __future__ import annotations
 
 import torch
 
-from .base import FeedForward, Part, Runtime, WeightSpec, to_compute
+from .base import FeedForward, Part, Runtime, WeightSpec, to_compute, to_f32_vector
 
 
 class RoutedExperts(FeedForward):
@@ -147,3 +147,80 @@ class RoutedExperts(FeedForward):
                 act = k.moe_expert_act(gu, none, 0, 8, 0.0, self.shared_limit, block=self.shared_block)
             shared = k.linear(act, self.shared_down, None, self.rt.dtype)
         return k.moe_combine(pairs, plan, shared, T, self.top, self.rt.dtype)
+
+
+class PlainRoutedExperts(FeedForward):
+    """y = sum over the token's chosen experts of w_e expert_e(x) (+ sigmoid(g . x) shared(x)), experts without a gate:
+    expert(x) = W_down act(W_up x), act the square of relu (or gelu_tanh, silu), no biases.
+
+    Router: logits z = W_r x and scores s = softmax(z) over all experts, in 32-bit.  The `top` experts with the largest
+    s + correction are chosen (a vector of one number per expert that bears on the choice only; the lower index on a
+    tie); a chosen expert weighs w_e = s_e * scale, not renormalised.  A shared expert of the same form and a width of
+    its own runs for every token and is added times sigmoid(g . x), one number per token.
+
+    All experts run side by side: the up matrices are stacked into one matrix and the down matrices laid side by side;
+    the activation kernel zeroes the columns of experts a token did not choose and multiplies the others by the token's
+    weight (the shared columns by the token's gate), and one product with the down matrices gives the weighted sum inside
+    the product's 32-bit accumulators.  The router's matrix and the shared gate's vector are stacked too, so that one
+    32-bit product gives a token's logits and its gate.  Nothing loops on the host and no token's result depends on what
+    else is in the batch, so a decode step can be captured.
+
+    Tensors, under `name`: router, correction; e<i>.up, e<i>.down; shared.up, shared.down, shared.sg."""
+
+    supports_cuda_graph = True
+
+    def __init__(self, width: int, experts: int, top: int, ff: int, name: str, scale: float = 1.0, shared_ff: int = 0,
+                 activation: str = "relu2", correction: str | None = "correction", shared_gate: str | None = "sg",
+                 weight_suffix: str = "", expert_prefix: str = "e", shared_name: str = "shared", router_name: str = "router",
+                 proj_names=("up", "down")):
+        if activation not in ("relu2", "gelu_tanh", "silu"):
+            raise ValueError(f"unknown activation {activation!r}")
+        if not 0 < top <= experts:
+            raise ValueError(f"top={top} of {experts} experts")
+        self.width, self.E, self.top, self.ff, self.scale = int(width), int(experts), int(top), int(ff), float(scale)
+        self.shared_ff, self.activation = int(shared_ff), activation
+        self.F = self.E * self.ff + self.shared_ff
+        u, d = proj_names
+        pre = [f"{name}.{expert_prefix}{i}" for i in range(self.E)] + ([f"{name}.{shared_name}"] if self.shared_ff else [])
+        widths = [self.ff] * self.E + ([self.shared_ff] if self.shared_ff else [])
+        self.up_names = [(f"{p}.{u}{weight_suffix}", w) for p, w in zip(pre, widths)]
+        self.down_names = [(f"{p}.{d}{weight_suffix}", w) for p, w in zip(pre, widths)]
+        self.router_name = f"{name}.{router_name}{weight_suffix}"
+        self.correction_name = f"{name}.{correction}" if correction else None
+        self.gate_name = f"{name}.{shared_name}.{shared_gate}{weight_suffix}" if self.shared_ff and shared_gate else None
+
+    def own_weight_specs(self):
+        specs = [WeightSpec(self.router_name, (self.E, self.width), "matrix")]
+        if self.correction_name:
+            specs.append(WeightSpec(self.correction_name, (self.E,), "bias"))
+        specs += [WeightSpec(n, (w, self.width), "matrix") for n, w in self.up_names]
+        specs += [WeightSpec(n, (self.width, w), "matrix") for n, w in self.down_names]
+        if self.gate_name:
+            specs.append(WeightSpec(self.gate_name, (1, self.width), "matrix"))
+        return specs
+
+    def bind_own(self, tensors, rt: Runtime):
+        rows = [to_compute(tensors[self.router_name], rt)]
+        if self.gate_name:
+            rows.append(to_compute(tensors[self.gate_name], rt).reshape(1, self.width))
+        if len({r.dtype for r in rows}) > 1:
+            rows = [r.float() for r in rows]
+        self.router = torch.cat(rows, 0).contiguous()             # [E (+1), width]: the experts' logits, then the shared gate's
+        self.correction = to_f32_vector(tensors[self.correction_name], rt) if self.correction_name else None
+        ups = [to_compute(tensors[n], rt) for n, _ in self.up_names]
+        downs = [to_compute(tensors[n], rt) for n, _ in self.down_names]
+        if len({m.dtype for m in ups + downs}) > 1:
+            ups, downs = [m.float() for m in ups], [m.float() for m in downs]
+        self.up = torch.cat(ups, 0).contiguous()                  # [F, width]
+        self.down = torch.cat(downs, 1).contiguous()              # [width, F]
+
+    def weight_bytes(self):
+        return sum(t.numel() * t.element_size() for t in (self.router, self.up, self.down))
+
+    def forward(self, x, ctx):
+        k = self.rt.k
+        z = k.linear(x, self.router, None, torch.float32)
+        w = k.moe_route(z, self.top, experts=self.E, correction=self.correction, scale=self.scale)
+        hidden = k.linear(x, self.up, None, self.rt.dtype)
+        act = k.moe_plain_act(hidden, w, self.E, self.ff, self.activation, shared_gate=z[:, self.E:] if self.gate_name else None)
+        return k.linear(act, self.down, None, self.rt.dtype)

@@ -333,9 +333,10 @@ def sigmoid_gate(o, gate, group=1):
     return o
 
 
-def moe_route(logits, top, groups=1, keep=1, want_chosen=False):
-    T, E = logits.shape
-    s = torch.softmax(logits.to(torch.float32), -1)
+def moe_route(logits, top, groups=1, keep=1, want_chosen=False, experts=None, correction=None, scale=1.0):
+    T, E = logits.shape[0], int(experts if experts is not None else logits.shape[1])
+    s = torch.softmax(logits[:, :E].to(torch.float32), -1)
+    pick = s if correction is None else s + correction.to(torch.float32)
     w = torch.zeros(T, E, dtype=torch.float32)
     chosen = torch.full((T, top), -1, dtype=torch.int32)
     for t in range(T):
@@ -345,11 +346,108 @@ def moe_route(logits, top, groups=1, keep=1, want_chosen=False):
             best = [max(float(s[t, e]) for e in range(g * per, (g + 1) * per)) for g in range(groups)]
             kept = sorted(range(groups), key=lambda g: (-best[g], g))[:keep]
             ok = [e // per in kept for e in range(E)]
-        order = sorted((e for e in range(E) if ok[e]), key=lambda e: (-float(s[t, e]), e))[:top]
+        order = sorted((e for e in range(E) if ok[e]), key=lambda e: (-float(pick[t, e]), e))[:top]
         for i, e in enumerate(order):
-            w[t, e] = s[t, e]
+            w[t, e] = s[t, e] * scale
             chosen[t, i] = e
     return (w, chosen) if want_chosen else w
+
+
+def moe_plain_act(u, weights, E, ff, act, shared_gate=None, out=None):
+    T, F = u.shape
+    x = u.to(F64)
+    if act == "relu2":
+        a = torch.relu(x) ** 2
+    elif act == "gelu_tanh":
+        a = 0.5 * x * (1.0 + torch.tanh(0.7978845608028654 * (x + 0.044715 * x ** 3)))
+    else:
+        a = _silu(x)
+    w = weights.to(F64).repeat_interleave(ff, dim=1)
+    if F > E * ff:
+        sg = torch.sigmoid(shared_gate[:, :1].to(F64)) if shared_gate is not None else torch.ones(T, 1, dtype=F64)
+        w = torch.cat([w, sg.expand(T, F - E * ff)], 1)
+    res = (a * w).to(u.dtype)
+    if out is not None:
+        out.copy_(res)
+        return out
+    return res
+
+
+def embed_scaled(ids, table, scale, status):
+    if ((ids < 0) | (ids >= table.shape[0])).any():
+        status[0] = 1
+        ids = ids.clamp(0, table.shape[0] - 1)
+    return (table[ids.long()].to(F64) * scale).to(torch.float32)
+
+
+def rmsnorm_pair_mean(a, b, wa, wb, eps, out_dtype):
+    def n(x, w):
+        x = x.to(F64)
+        return x / torch.sqrt((x * x).mean(-1, keepdim=True) + eps) * w.to(F64)
+    return (0.5 * (n(a, wa) + n(b, wb))).to(out_dtype)
+
+
+def retention_prepare(proj, positions, inv_freq, decay, H, D, P, rot, k_scale):
+    T = proj.shape[0]
+    row = proj.to(F64)
+    q = _rotate(row[:, :H * D].reshape(T, H, D), positions, inv_freq, rot, False)
+    k = _rotate(row[:, H * D:2 * H * D].reshape(T, H, D), positions, inv_freq, rot, False) * k_scale
+    v = row[:, 2 * H * D:2 * H * D + H * P]
+    xbc = torch.cat([v, k.reshape(T, -1), q.reshape(T, -1)], 1).to(torch.float32)
+    dd = torch.cat([torch.ones(T, H), decay.to(torch.float32)[None, :].expand(T, H)], 1).contiguous()
+    return xbc, dd
+
+
+def retention_gate_norm(o, gate, eps, H, P, out_dtype, out=None):
+    T = o.shape[0]
+    v = o.to(F64).reshape(T, H, P)
+    v = (v / torch.sqrt((v * v).mean(-1, keepdim=True) + eps)).reshape(T, H * P) * _silu(gate.to(F64))
+    res = v.to(out_dtype)
+    if out is not None:
+        out.copy_(res)
+        return out
+    return res
+
+
+def sigmoid_attention(q, kv, ctx, group, nh, nkv, hd, vd, scale, softcap, window, page_size, head_bias, mix, out=None,
+                      out_dtype=None):
+    T = q.shape[0]
+    flat = kv.reshape(-1)
+    part = torch.zeros(T, nh, nkv, vd, dtype=F64)              # head g's weights over the values of key/value head c
+    rep = nh // nkv
+    page_elems = nkv * page_size * (hd + vd)
+    for t in range(T):
+        pos = int(ctx.positions[t])
+        if pos < 0:
+            continue
+        bt = group.block_tables[int(ctx.token_row[t])]
+        lo = max(0, pos - window + 1) if window > 0 else 0
+        js = torch.arange(lo, pos + 1)
+        pages = bt[(js // page_size).long()].long()
+        if (pages < 0).any():
+            ctx.status[0] = 3
+            continue
+        Ks, Vs = [], []
+        for c in range(nkv):
+            at = pages * page_elems + (c * page_size + js % page_size) * hd
+            Ks.append(flat[at[:, None] + torch.arange(hd)[None, :]].to(F64))
+            at = pages * page_elems + nkv * page_size * hd + (c * page_size + js % page_size) * vd
+            Vs.append(flat[at[:, None] + torch.arange(vd)[None, :]].to(F64))
+        for h in range(nh):
+            s = (Ks[h // rep] @ q[t, h * hd:(h + 1) * hd].to(F64)) * scale
+            if softcap and softcap > 0:
+                s = softcap * torch.tanh(s / softcap)
+            w = torch.sigmoid(s + (head_bias[h].to(F64) if head_bias is not None else 0.0))
+            for c in range(nkv):
+                part[t, h, c] = w @ Vs[c]
+    res = torch.zeros(T, nh, vd, dtype=F64)
+    for h in range(nh):
+        res[:, h] = torch.einsum("g,tgv->tv", mix[h].to(F64), part[:, :, h // rep])
+    res = res.reshape(T, nh * vd).to(out_dtype or kv.dtype)
+    if out is not None:
+        out.copy_(res)
+        return out
+    return res
 
 
 def moe_expert_act(gu, weights, E, ff, limit, limit_shared=0.0, out=None, block=0):
