@@ -156,6 +156,36 @@ __global__ void moe_expert_act_vec_kernel(const bf16* gu, long long gu_stride, c
     *reinterpret_cast<uint4*>(out + r * out_stride + c) = o;
   }
 }
+
+// Experts without a gate, side by side: u[t] holds F = E * ff (+ a shared expert's) hidden values; y = w * act(u) with w
+// the token's weight for the column's expert, zero where it did not choose it.  The shared columns at the end weigh
+// sigmoid(shared_gate[t]) where a gate is given, else 1.  act: 0 relu^2, 1 gelu (tanh form), 2 silu.
+template <typename T>
+__global__ void moe_plain_act_kernel(const T* u, long long u_stride, const float* weights, const float* shared_gate,
+                                     long long sg_stride, T* out, long long out_stride, long long rows, int E, int ff, int F,
+                                     int act) {
+  pdl_wait();
+  pdl_trigger();
+  const long long n = rows * F;
+  for (long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x; idx < n; idx += (long long)gridDim.x * blockDim.x) {
+    const long long r = idx / F;
+    const int c = (int)(idx - r * F);
+    const int e = c / ff;
+    float w;
+    if (e < E) w = weights[r * E + e];
+    else w = shared_gate != nullptr ? 1.0f / (1.0f + expf(-shared_gate[r * sg_stride])) : 1.0f;
+    float y = 0.f;
+    if (w != 0.f) {
+      const float x = to_f(u[r * u_stride + c]);
+      float a;
+      if (act == 0) { const float p = fmaxf(x, 0.f); a = p * p; }
+      else if (act == 1) a = 0.5f * x * (1.0f + tanhf(0.7978845608028654f * (x + 0.044715f * x * x * x)));
+      else a = x / (1.0f + expf(-x));
+      y = w * a;
+    }
+    out[r * out_stride + c] = from_f<T>(y);
+  }
+}
 }  // namespace
 
 // choice_bias ([E], may be null): added to the scores for the choice only; weight_scale multiplies the chosen scores.
@@ -206,6 +236,27 @@ FMX_EXPORT int fmx_moe_expert_act(const void* gu, long long gu_stride, const flo
                out_stride, (long long)rows, E, ff, F, limit, limit_shared, gu_block);
   else
     return fmx_fail("fmx_moe_expert_act: unknown dtype %d", dtype);
+  FMX_LAUNCH_CHECK();
+  return 0;
+}
+
+FMX_EXPORT int fmx_moe_plain_act(const void* u, long long u_stride, const float* weights, const float* shared_gate,
+                                 long long sg_stride, void* out, long long out_stride, int rows, int E, int ff, int F, int act,
+                                 int dtype, cudaStream_t stream) {
+  if (rows == 0 || F == 0) return 0;
+  if (rows < 0 || E < 0 || ff <= 0 || F < E * ff || u_stride < F || out_stride < F || act < 0 || act > 2)
+    return fmx_fail("fmx_moe_plain_act: bad sizes rows=%d E=%d ff=%d F=%d act=%d", rows, E, ff, F, act);
+  const long long n = (long long)rows * F, cap = (long long)fmx_num_sms() * 16;
+  const int block = 256;
+  const int grid = (int)((n + block - 1) / block < cap ? (n + block - 1) / block : cap);
+  if (dtype == FMX_F32)
+    fmx_launch(moe_plain_act_kernel<float>, dim3(grid), dim3(block), 0, stream, (const float*)u, u_stride, weights, shared_gate,
+               sg_stride, (float*)out, out_stride, (long long)rows, E, ff, F, act);
+  else if (dtype == FMX_BF16)
+    fmx_launch(moe_plain_act_kernel<bf16>, dim3(grid), dim3(block), 0, stream, (const bf16*)u, u_stride, weights, shared_gate,
+               sg_stride, (bf16*)out, out_stride, (long long)rows, E, ff, F, act);
+  else
+    return fmx_fail("fmx_moe_plain_act: unknown dtype %d", dtype);
   FMX_LAUNCH_CHECK();
   return 0;
 }
