@@ -25,6 +25,9 @@ GROUPS = {
     "common": "common",
     "bf16": "bf16",
     "attn": "attn",
+    # "mixattn_v2_p4": the tiled attention with mixed heads, compiled with -DFMX_VPL=2 -DFMX_PER=4: one library per
+    # (values per lane, query heads per key head), built when a model of those sizes is met
+    "mixattn": "mixattn",
     "tc": "tc",
     # host code: the native step executor (no kernel of its own)
     "host": "host",
@@ -34,6 +37,7 @@ GROUPS = {
 }
 EXTRA_FLAGS = {"tc_expiry": ["-DFMX_WAIT_CYCLES=100000LL", "-DFMX_SKIP_LAST_STAGE=1"]}
 HEAD_DIMS = tuple(range(16, 257, 16))
+MIXATTN_SIZES = (1, 2, 4, 8)          # values per lane (value heads up to 32 times that), and query heads per key head
 
 
 def _split(group: str) -> tuple[str, list[str]]:
@@ -43,6 +47,15 @@ def _split(group: str) -> tuple[str, list[str]]:
         if hd not in HEAD_DIMS:
             raise BuildError(f"the tiled attention kernels take head sizes in steps of 16 up to 256, not {hd}")
         return "attn", [f"-DFMX_HD={hd}"]
+    if group.startswith("mixattn_v"):
+        try:
+            vpl, per = (int(x) for x in group[len("mixattn_v"):].split("_p"))
+        except ValueError:
+            raise BuildError(f"unknown kernel group {group!r}") from None
+        if vpl not in MIXATTN_SIZES or per not in MIXATTN_SIZES:
+            raise BuildError(f"the attention with mixed heads is built for {MIXATTN_SIZES} values per lane and heads per "
+                             f"key head, not {vpl} and {per}")
+        return "mixattn", [f"-DFMX_VPL={vpl}", f"-DFMX_PER={per}"]
     if group not in GROUPS:
         raise BuildError(f"unknown kernel group {group!r}")
     return group, list(EXTRA_FLAGS.get(group, ()))
@@ -171,7 +184,8 @@ def build(group: str, force: bool = False, verbose: bool = False) -> str:
 
 def build_all(force: bool = False, verbose: bool = False, head_dims=HEAD_DIMS) -> list[str]:
     """Every library: the plain groups and the attention kernels of every head size."""
-    groups = [g for g in GROUPS if g != "attn" and sources(g)] + [f"attn_hd{hd}" for hd in head_dims]
+    groups = [g for g in GROUPS if g not in ("attn", "mixattn") and sources(g)] + [f"attn_hd{hd}" for hd in head_dims] + \
+        [f"mixattn_v{v}_p{p}" for v in MIXATTN_SIZES for p in MIXATTN_SIZES]
     with ThreadPoolExecutor(max_workers=max(1, (os.cpu_count() or 2) // 2)) as ex:
         return list(ex.map(lambda g: build(g, force, verbose), groups))
 

@@ -705,12 +705,36 @@ def retention_gate_norm(o, gate, eps: float, H: int, P: int, out_dtype, out=None
     return out
 
 
+def _pow2_at_least(n: int, choices=(1, 2, 4, 8)) -> int:
+    for c in choices:
+        if n <= c:
+            return c
+    return 0
+
+
+def mixed_heads_library(nh: int, nkv: int, hd: int, vd: int, q=None, kv=None) -> str | None:
+    """The library of the tiled attention with mixed heads that takes these sizes (one per values-per-lane and query
+    heads per key head), or None: 32-bit queries over bfloat16 pages, values up to 256 wide, at most 8 query heads per
+    key head."""
+    if kv is not None and (kv.dtype != torch.bfloat16 or q is None or q.dtype != torch.float32):
+        return None
+    if q is not None and (q.data_ptr() % 16 or q.stride(0) % 4 or (nh * hd) % 4):
+        return None
+    vpl, per = _pow2_at_least(-(-vd // 32)), _pow2_at_least(nh // nkv)
+    return f"mixattn_v{vpl}_p{per}" if vpl and per else None
+
+
 def sigmoid_attention(q, kv, ctx, group, nh, nkv, hd, vd, scale, softcap, window, page_size, head_bias, mix, out=None,
-                      out_dtype=None) -> torch.Tensor:
+                      out_dtype=None, tiled: bool | None = None) -> torch.Tensor:
     """Attention without a softmax: a visible key weighs sigmoid(cap(scale q.k) + head_bias[head]); the heads' weights are
     mixed by `mix` ([nh, nh], 32-bit: row h lists what head h takes of every head's weights) and head h applies its mixed
     weights to the values of its own key/value head.  Queries q[T, nh*hd] of their own type over pages of [nkv, page, hd]
-    keys and [nkv, page, vd] values; scores, weights and the sums over keys are 32-bit.  -> [T, nh*vd]."""
+    keys and [nkv, page, vd] values; scores, weights and the sums over keys are 32-bit.  -> [T, nh*vd].
+
+    Two kernels: over bfloat16 pages a block owns all heads of a tile of tokens and mixes the weights before they meet
+    the values (prompt portions and single tokens; a single token's keys may be shared out over several blocks); else,
+    and on the 32-bit path, one warp per (token, head, value head) sums the unmixed heads' outputs, which a second
+    kernel mixes.  `tiled`: force the choice (None: the tiled kernel where it takes the sizes)."""
     _need_cuda(q, kv, head_bias, mix, out)
     assert kv.is_contiguous() and q.stride(1) == 1
     T = q.shape[0]
@@ -720,6 +744,19 @@ def sigmoid_attention(q, kv, ctx, group, nh, nkv, hd, vd, scale, softcap, window
     assert mix.dtype == torch.float32 and mix.is_contiguous() and mix.shape == (nh, nh)
     assert head_bias is None or (head_bias.dtype == torch.float32 and head_bias.numel() == nh)
     bt = group.block_tables
+    name = mixed_heads_library(nh, nkv, hd, vd, q, kv) if tiled is not False and out.dtype == torch.bfloat16 else None
+    if name is not None:
+        lib = load(name)
+        splits = int(lib.fmx_mixattn_plan(T, nh, nkv, hd, vd, int(ctx.max_q_len), int(ctx.max_ctx_after)))
+        if splits > 0:
+            part = torch.empty((splits, T, nh * vd), dtype=torch.float32, device=q.device) if splits > 1 else None
+            call(name, "fmx_mixattn", q.data_ptr(), q.stride(0), kv.data_ptr(), bt.data_ptr(), bt.stride(0),
+                 ctx.token_row.data_ptr(), ctx.positions.data_ptr(), ctx.row_start.data_ptr(), _ptr(part), out.data_ptr(),
+                 out.stride(0), T, nh, nkv, hd, vd, int(page_size), kv.shape[0], float(scale), float(softcap or 0.0),
+                 int(window), bt.shape[0], _ptr(head_bias), mix.data_ptr(), int(ctx.max_q_len), splits, _ptr(ctx.status),
+                 _stream())
+            return out
+    assert tiled is not True, "the tiled kernel does not take these sizes"
     part = torch.empty((T, nh, nkv, vd), dtype=torch.float32, device=q.device)
     call("common", "fmx_sigmoid_attention", q.data_ptr(), q.stride(0), _dt(q), kv.data_ptr(), bt.data_ptr(), bt.stride(0),
          ctx.token_row.data_ptr(), ctx.positions.data_ptr(), part.data_ptr(), T, nh, nkv, hd, vd, int(page_size), kv.shape[0],

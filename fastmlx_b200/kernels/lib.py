@@ -82,6 +82,10 @@ _SIGNATURES = {
         "fmx_expert_tcgen05": [_P, _L, _P, _L, _P, _L, _I, _I, _I, _F, _I, _P, _P],
         "fmx_grouped_tcgen05": [_P, _L, _P, _L, _P, _L, _I, _I, _I, _I, _P, _P, _P, _P, _F, _I, _I, _P, _P],
     },
+    "mixattn": {
+        "fmx_mixattn": [_P, _L, _P, _P, _I, _P, _P, _P, _P, _P, _L, _I, _I, _I, _I, _I, _I, _L, _F, _F, _I, _I, _P, _P, _I, _I, _P, _P],
+        "fmx_mixattn_plan": [_I, _I, _I, _I, _I, _I, _I],
+    },
     "attn": {
         "fmx_attn_prefill_tc": [_P, _L, _I, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _L, _F, _I, _P, _I, _P, _L, _P],
         "fmx_attn_prefill": [_P, _L, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _L, _F, _I, _P, _P],
@@ -125,7 +129,8 @@ def load(group: str) -> ctypes.CDLL:
         lib.fmx_gemm_tcgen05_plan_width.argtypes = [_I, _I, _I]
         lib.fmx_gemm_tcgen05_plan_fills.argtypes = [_I, _I, _I]
     lib.fmx_last_error.restype = ctypes.c_char_p
-    family = "attn" if group.startswith("attn_hd") else "tc" if group == "tc_expiry" else group
+    family = "attn" if group.startswith("attn_hd") else "tc" if group == "tc_expiry" else \
+        "mixattn" if group.startswith("mixattn_v") else group
     for name, args in _SIGNATURES.get(family, {}).items():
         fn = getattr(lib, name)
         fn.argtypes = args
