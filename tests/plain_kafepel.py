@@ -126,14 +126,19 @@ def expert(h, W):
     return (torch.relu(h @ W["up"].T) ** 2) @ W["down"].T
 
 
-def routed_feed_forward(h, W, mlp):
+def routed_feed_forward(h, W, mlp, margins=None):
     """softmax scores over all experts; the `top` largest of score + correction are chosen; a chosen expert weighs
-    score * router.scale (no renormalisation); the shared expert is added times sigmoid(sg . h)."""
+    score * router.scale (no renormalisation); the shared expert is added times sigmoid(sg . h).  `margins`, a list,
+    receives [T]: by how much (in choice scores) each token's choice is decided, the gap between the last expert
+    chosen and the first one left out (infinite where all are chosen)."""
     r = mlp["router"]
     E, top = int(r["experts"]), int(r["top"])
     s = torch.softmax(h @ W["router"].T, dim=-1)
     choice = s + W["correction"] if "correction" in W else s
     idx = torch.topk(choice, top, dim=-1).indices                    # [T, top]
+    if margins is not None:
+        ranked = torch.sort(choice, dim=-1, descending=True).values
+        margins.append(ranked[:, top - 1] - ranked[:, top] if top < E else torch.full_like(ranked[:, 0], float("inf")))
     out = torch.zeros_like(h)
     for t in range(h.shape[0]):
         for e in idx[t].tolist():
@@ -144,8 +149,9 @@ def routed_feed_forward(h, W, mlp):
     return out
 
 
-def forward(cfg, tensors, ids, dtype=torch.float64, return_layers=False):
-    """Logits [T, vocab] of one whole sequence; with `return_layers` also the stream after every layer."""
+def forward(cfg, tensors, ids, dtype=torch.float64, return_layers=False, margins=None):
+    """Logits [T, vocab] of one whole sequence; with `return_layers` also the stream after every layer; `margins`, a
+    list, receives every router's margins (see `routed_feed_forward`)."""
     W = {k: v.to(dtype) if v.is_floating_point() else v for k, v in tensors.items()}
     ids = torch.as_tensor(ids, dtype=torch.long)
     eps = float(cfg["norm"]["eps"])
@@ -159,7 +165,7 @@ def forward(cfg, tensors, ids, dtype=torch.float64, return_layers=False):
         if mlp is not None:
             h = rms_norm(x, eps, W[f"l{i}.norm2"])
             w = sub(W, f"l{i}.mlp.")
-            x = x + (dense_feed_forward(h, w) if mlp["kind"] == "dense" else routed_feed_forward(h, w, mlp))
+            x = x + (dense_feed_forward(h, w) if mlp["kind"] == "dense" else routed_feed_forward(h, w, mlp, margins))
         streams.append(x)
     logits = rms_norm(x, eps, W["final.norm"]) @ W["head"].T
     return (logits, torch.stack(streams)) if return_layers else logits
