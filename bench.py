@@ -440,6 +440,25 @@ def sorupel_like(shape: dict, layers: int, chunk: int = 1024) -> dict:
             "embedding": {"bigram": {"buckets": 99991, "mul_prev": 31337, "mul_cur": 7919}}, "layers": out}
 
 
+def kafepel_like(shape: dict, layers: int) -> dict:
+    """A Kafepel configuration with a Llama shape's width, heads and vocabulary: every layer a pair of mixers side by side,
+    sigmoid attention with mixed heads (the shape's heads and key/value heads, capped scores, the whole head rotated with
+    rescaled frequency bands, every earlier key in sight) beside a retention of as many heads of the same size (decays
+    spread from 1 - 2^-5 to 1 - 2^-8); feed-forwards alternate between the Llama layer's gated one and a mixture of 8
+    squared-relu experts, 2 per token, each a quarter of the gated feed-forward's hidden size, with a gated shared expert
+    of half of it."""
+    d, nh, nkv, hd = shape["hidden_size"], shape["num_attention_heads"], shape["num_key_value_heads"], shape["head_dim"]
+    ff = shape["intermediate_size"]
+    rot = {"dims": hd, "base": 1000000.0, "scaling": {"factor": 8.0, "low": 1.0, "high": 4.0, "original": 8192}}
+    mixer = {"left": {"heads": nh, "kv_heads": nkv, "dim": hd, "vdim": hd, "scale": hd ** -0.5, "softcap": 50.0, "rot": rot},
+             "right": {"heads": nh, "dim": hd, "vdim": hd, "decay": [1.0 - 2.0 ** -(5 + 3 * i / max(1, nh - 1)) for i in range(nh)],
+                       "rot": {"dims": hd, "base": 1000000.0}}}
+    dense = {"kind": "dense", "ff": ff}
+    moe = {"kind": "moe", "router": {"experts": 8, "top": 2, "scale": 2.5}, "expert": {"ff": ff // 4}, "shared": {"ff": ff // 2}}
+    return {"architecture": "Kafepel", "vocab": shape["vocab_size"], "width": d, "norm": {"eps": 1e-6}, "embedding": {"scale": 0.5},
+            "layers": [{"type": "parallel", "mixer": mixer, "mlp": moe if i % 2 else dense} for i in range(layers)]}
+
+
 def step_weight_bytes(model, tokens: int) -> int:
     """Bytes of weights a step of `tokens` tokens must read: every run of the schedule reads its layer (a looped layer
     once per pass); a routed feed-forward with grouped products reads the experts its tokens chose, at most."""
@@ -505,7 +524,8 @@ def compare_designs(shapes, layers: int, context: int, steps: int, warmup: int, 
     for key in shapes:
         name, shape = SHAPES[key]
         make = {"llama": lambda: dict(shape, num_hidden_layers=layers), "medirax": lambda: medirax_like(shape, layers),
-                "gekavik": lambda: gekavik_like(shape, layers), "sorupel": lambda: sorupel_like(shape, layers)}
+                "gekavik": lambda: gekavik_like(shape, layers), "sorupel": lambda: sorupel_like(shape, layers),
+                "kafepel": lambda: kafepel_like(shape, layers)}
         out[key] = {"layers": layers, "context": context}
         for design in which:
             out[key][design] = design_numbers(make[design](), shape["vocab_size"], pk, context, steps, warmup)
@@ -557,13 +577,14 @@ def main() -> int:
     if args.designs:
         keys = [k for k in args.designs.split(",") if k]
         which = [w for w in args.design_set.split(",") if w]
-        if any(w not in ("llama", "medirax", "gekavik", "sorupel") for w in which):
-            print(f"bench.py: --design-set takes llama, medirax, gekavik, sorupel (got {args.design_set!r})")
+        if any(w not in ("llama", "medirax", "gekavik", "sorupel", "kafepel") for w in which):
+            print(f"bench.py: --design-set takes llama, medirax, gekavik, sorupel, kafepel (got {args.design_set!r})")
             return 2
         if args.only_steps > 0:
             shape = SHAPES[keys[0]][1]
             make = {"llama": lambda: dict(shape, num_hidden_layers=args.design_layers), "medirax": lambda: medirax_like(shape, args.design_layers),
-                    "gekavik": lambda: gekavik_like(shape, args.design_layers), "sorupel": lambda: sorupel_like(shape, args.design_layers)}
+                    "gekavik": lambda: gekavik_like(shape, args.design_layers), "sorupel": lambda: sorupel_like(shape, args.design_layers),
+                    "kafepel": lambda: kafepel_like(shape, args.design_layers)}
             design_steps(make[which[0]](), shape["vocab_size"], args.batch, min(args.context, 4096), args.only_steps, warmup,
                          not args.no_cuda_graphs)
             print(f"ran a {PREFILL_TOKENS}-token prompt step and {args.only_steps} decode steps of batch {args.batch} of {which[0]} at the {keys[0]} sizes")

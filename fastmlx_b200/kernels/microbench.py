@@ -8,6 +8,7 @@ launches), for tuning and for profiler captures on a small case.
     python -m fastmlx_b200.kernels.microbench --kernel sample --batch 8 --N 128256
     python -m fastmlx_b200.kernels.microbench --kernel recurrence --batch 1 --qlen 2048 --nh 64 --hd 64 --state 128
     python -m fastmlx_b200.kernels.microbench --kernel attn_masked --batch 64 --qlen 1 --ctx 4096 --hd 64
+    python -m fastmlx_b200.kernels.microbench --kernel attn_mixed --batch 64 --qlen 1 --ctx 4096 --hd 64
 """
 from __future__ import annotations
 
@@ -173,9 +174,57 @@ def _attn_masked(a) -> int:
     return 0
 
 
+def _attn_mixed(a) -> int:
+    """Sigmoid attention whose heads' weights are mixed (the tiled kernel that owns all heads of a tile of tokens, and
+    with --simple also the kernel of one warp per token, head and value head), and a retention's three kernels
+    (prepare, the state-space scan with a group per head, gated norm per head) at the same head sizes: --batch requests
+    of --qlen tokens behind --ctx tokens."""
+    B, q, c, nh, nkv, hd, ps = a.batch, a.qlen, a.ctx if a.ctx != 8192 or a.qlen == 1 else 0, a.nh, a.nkv, a.hd, a.page
+    ctx = _rows_ctx(B, q, c)
+    per = -(-(c + q) // ps)
+    flush = _flush()
+    grp = SimpleNamespace(block_tables=torch.randperm(B * per + 8, device=DEV)[:B * per].int().view(B, per).contiguous(), page_size=ps)
+    kv = torch.randn(B * per + 8, 2, nkv, ps, hd, device=DEV).bfloat16()
+    qq = torch.randn(B * q, nh * hd, device=DEV)
+    mix = (torch.eye(nh, device=DEV) + 0.1 * torch.randn(nh, nh, device=DEV)).contiguous()
+    bias = torch.randn(nh, device=DEV) - 3.0
+    every = sum(p + 1 for p in range(c, c + q)) * B                          # (query, key) pairs in sight
+    fma = every * (nh * hd + nh * nh + nh * hd)                              # scores, the mix, the values: 32-bit multiply-adds
+    kvb = B * (c + q) * nkv * hd * 2 * 2
+    cases = [("tiled", lambda: k.sigmoid_attention(qq, kv, ctx, grp, nh, nkv, hd, hd, hd ** -0.5, 50.0, 0, ps, bias, mix, tiled=True))]
+    if a.simple:
+        cases.append(("one warp per token, head and value head",
+                      lambda: k.sigmoid_attention(qq, kv, ctx, grp, nh, nkv, hd, hd, hd ** -0.5, 50.0, 0, ps, bias, mix, tiled=False)))
+    for name, fn in cases:
+        us = _time_events(fn, a.replays, flush)
+        print(f"attn_mixed {name} B={B} qlen={q} ctx={c} nh={nh} nkv={nkv} hd={hd}: {us:.1f} us, {fma / us / 1e6:.2f} TFMA/s of "
+              f"32-bit multiply-adds, {kvb / us / 1e3:.0f} GB/s of keys and values")
+    # ---- the retention beside it: nh heads of hd values over hd rows of state
+    H, D, P, T = nh, hd, hd, B * q
+    proj = torch.randn(T, 2 * H * D + 2 * H * P, device=DEV)
+    inv = torch.rand(D // 2, device=DEV)
+    decay = torch.rand(H, device=DEV) * 0.1 + 0.9
+    state = torch.randn(B, H * P * D, device=DEV) * 0.1
+    zero = torch.zeros(H, device=DEV)
+    xbc, dd = k.retention_prepare(proj, ctx.positions, inv, decay, H, D, P, D, D ** -0.5)
+    o = k.ssm_scan(xbc, dd, zero, ctx, state, H, H, D, P)
+    rows = [("retention_prepare", lambda: k.retention_prepare(proj, ctx.positions, inv, decay, H, D, P, D, D ** -0.5),
+             T * (2 * H * D + H * P) * 8 + T * 2 * H * 4),
+            ("ssm_scan, a group per head", lambda: k.ssm_scan(xbc, dd, zero, ctx, state, H, H, D, P),
+             2 * B * H * P * D * 4 + T * (2 * H * D + 2 * H * P + 2 * H) * 4),
+            ("retention_gate_norm", lambda: k.retention_gate_norm(o, proj[:, 2 * H * D + H * P:], 1e-6, H, P, torch.bfloat16),
+             T * H * P * (4 + 4 + 2))]
+    for name, fn, nbytes in rows:
+        us = _time_events(fn, a.replays, flush)
+        print(f"{name} B={B} qlen={q} heads={H} dim={D} vdim={P}: {us:.1f} us, {nbytes / 1e6:.1f} MB, {nbytes / us / 1e3:.0f} GB/s")
+    print("status", ctx.status.tolist())
+    return 0
+
+
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser(description=__doc__.split("\n\n")[0])
-    ap.add_argument("--kernel", required=True, choices=["attn_decode", "attn_prefill", "gemv", "gemm", "sample", "recurrence", "attn_masked"])
+    ap.add_argument("--kernel", required=True, choices=["attn_decode", "attn_prefill", "gemv", "gemm", "sample", "recurrence", "attn_masked", "attn_mixed"])
+    ap.add_argument("--simple", action="store_true", help="attn_mixed: time the kernel of one warp per token, head and value head too")
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--ctx", type=int, default=8192, help="tokens already in the cache")
     ap.add_argument("--qlen", type=int, default=2048, help="tokens per row (attn_prefill)")
@@ -201,6 +250,8 @@ def main(argv=None) -> int:
         return _recurrence(a)
     if a.kernel == "attn_masked":
         return _attn_masked(a)
+    if a.kernel == "attn_mixed":
+        return _attn_mixed(a)
     if a.kernel == "attn_decode":
         qkv, kv, ctx, grp = _attention_inputs(a, 1)
         splits = a.splits or k.decode_splits(a.batch, a.nkv, a.ctx + 1, a.hd)
