@@ -96,7 +96,7 @@ mixed_heads_attention_kernel(const float* q, long long q_stride, const bf16* kv,
   extern __shared__ __align__(16) unsigned char smem_raw[];
   pdl_wait();
   pdl_trigger();
-  const int t0 = blockIdx.x, split = blockIdx.y;
+  const int t0 = n_tokens - 1 - (int)blockIdx.x, split = blockIdx.y;      // a row's last tiles walk the most keys: they start first
   const int row = token_row[t0];
   if (row < 0 || row >= R) {
     if (threadIdx.x == 0) fmx_set_status(status, FMX_BAD_ROW, row, t0);
@@ -147,31 +147,54 @@ mixed_heads_attention_kernel(const float* q, long long q_stride, const bf16* kv,
   const float inv_cap = softcap > 0.f ? 1.0f / softcap : 0.f;
   const bool kvec = (hd & 7) == 0 && (vd & 7) == 0;
 
+  // the warp's units: (token of the tile, key/value head), the same for every tile of keys
+  int u_i[US], u_c[US];
+  bool u_on[US];
+#pragma unroll
+  for (int s = 0; s < US; ++s) {
+    const int n = warp + WARPS * s;
+    u_on[s] = n < n_q * nkv;
+    u_i[s] = u_on[s] ? n / nkv : 0;
+    u_c[s] = u_on[s] ? n - u_i[s] * nkv : 0;
+  }
+  // rows of a tile are copied by groups of lanes: `lpr` lanes (a power of two) take a row's 16-byte pieces
+  const int kc = hd / 8, vc = vd / 8, cpr = kc + vc;
+  int lpr_log = 0;
+  while ((1 << lpr_log) < cpr && lpr_log < 5) ++lpr_log;
+  const int lpr = 1 << lpr_log, rpi = 32 >> lpr_log;                 // lanes per row, rows per warp and pass
+  const int page_log = (page_size & (page_size - 1)) == 0 ? 31 - __clz(page_size) : -1;
+
   for (int kt = kt_first; kt < kt_end; ++kt) {
     __syncthreads();                                    // the tile before is done with K, V and P (and q, M are written)
     // ---- load: rows (c, jj) of keys and of values
     if (kvec) {
-      const int kc = hd / 8, vc = vd / 8;
-      for (int x = threadIdx.x; x < nkv * TK * (kc + vc); x += blockDim.x) {
-        const int r = x / (kc + vc), ch = x - r * (kc + vc);
+      // 16-byte asynchronous copies, all of a thread's in flight together; a row out of sight is filled with zeros
+      const int sub = lane >> lpr_log, ch0 = lane & (lpr - 1);
+      for (int r = warp * rpi + sub; r < nkv * TK; r += WARPS * rpi) {
         const int c = r / TK, jj = r - c * TK;
         const int j = kt * TK + jj;
-        uint4 val = make_uint4(0u, 0u, 0u, 0u);
+        const bf16* ksrc = nullptr;
+        const bf16* vsrc = nullptr;
         if (j >= lo_min && j <= pos_last) {
-          const int blk = j / page_size;
+          const int blk = page_log >= 0 ? j >> page_log : j / page_size;
           const int page = blk < bt_stride ? bt[blk] : -1;
           if (page < 0 || page >= num_pages) {
             fmx_set_status(status, FMX_BAD_PAGE, page, t0);
           } else {
             const long long at = (long long)c * page_size + (j - blk * page_size);
-            const bf16* src = ch < kc ? kv + (long long)page * page_elems + at * hd + ch * 8
-                                      : kv + (long long)page * page_elems + plane + at * vd + (ch - kc) * 8;
-            val = *reinterpret_cast<const uint4*>(src);
+            ksrc = kv + (long long)page * page_elems + at * hd;
+            vsrc = kv + (long long)page * page_elems + plane + at * vd;
           }
         }
-        bf16* dst = ch < kc ? Ks + (long long)r * KST + ch * 8 : Vs + (long long)r * VROW + (ch - kc) * 8;
-        *reinterpret_cast<uint4*>(dst) = val;
+        for (int ch = ch0; ch < cpr; ch += lpr) {
+          const bf16* src = ksrc == nullptr ? kv : (ch < kc ? ksrc + ch * 8 : vsrc + (ch - kc) * 8);
+          bf16* dst = ch < kc ? Ks + (long long)r * KST + ch * 8 : Vs + (long long)r * VROW + (ch - kc) * 8;
+          const unsigned sa = (unsigned)__cvta_generic_to_shared(dst);
+          asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(sa), "l"(src), "r"(ksrc == nullptr ? 0u : 16u));
+        }
       }
+      asm volatile("cp.async.commit_group;\n" ::);
+      asm volatile("cp.async.wait_group 0;\n" ::);
     } else {
       for (int x = threadIdx.x; x < nkv * TK * (hd + vd); x += blockDim.x) {
         const int r = x / (hd + vd), e = x - r * (hd + vd);
@@ -194,87 +217,139 @@ mixed_heads_attention_kernel(const float* q, long long q_stride, const bf16* kv,
       }
     }
     __syncthreads();
-    // ---- scores: P[i, h, key]
+    // ---- scores: P[i, h, key]; the units of a warp side by side, so that their chains of multiply-adds interleave
+    {
+      float dot[US][PER], dot2[US][PER];                  // a dot product as two chains: even and odd runs of eight dimensions
 #pragma unroll
-    for (int s = 0; s < US; ++s) {
-      const int n = warp + WARPS * s;
-      if (n >= n_q * nkv) break;
-      const int i = n / nkv, c = n - i * nkv;
-      const int pos_i = pos0 + i;
-      const int lo_i = window > 0 ? max(0, pos_i - window + 1) : 0;
-      const int j = kt * TK + lane;
-      const bool valid = j >= lo_i && j <= pos_i;
-      const bf16* krow = Ks + ((long long)c * TK + lane) * KST;
-      const float* qb = qs + ((long long)i * nh + (long long)c * per) * hd;
-      float dot[PER];
+      for (int s = 0; s < US; ++s)
 #pragma unroll
-      for (int hh = 0; hh < PER; ++hh) dot[hh] = 0.f;
+        for (int hh = 0; hh < PER; ++hh) dot[s][hh] = dot2[s][hh] = 0.f;
       if ((hd & 7) == 0) {
-        for (int e = 0; e < hd; e += 8) {
-          float kf[8];
-          load8(krow + e, kf);
+        auto run = [&](int e, float (&into)[US][PER]) {
 #pragma unroll
-          for (int hh = 0; hh < PER; ++hh) {
-            if (hh < per) {
-              const float4 a = *reinterpret_cast<const float4*>(qb + (long long)hh * hd + e);
-              const float4 b = *reinterpret_cast<const float4*>(qb + (long long)hh * hd + e + 4);
-              float d = dot[hh];
-              d = fmaf(a.x, kf[0], d); d = fmaf(a.y, kf[1], d); d = fmaf(a.z, kf[2], d); d = fmaf(a.w, kf[3], d);
-              d = fmaf(b.x, kf[4], d); d = fmaf(b.y, kf[5], d); d = fmaf(b.z, kf[6], d); d = fmaf(b.w, kf[7], d);
-              dot[hh] = d;
+          for (int s = 0; s < US; ++s) {
+            if (!u_on[s]) continue;
+            float kf[8];
+            load8(Ks + ((long long)u_c[s] * TK + lane) * KST + e, kf);
+            const float* qb = qs + ((long long)u_i[s] * nh + (long long)u_c[s] * per) * hd + e;
+#pragma unroll
+            for (int hh = 0; hh < PER; ++hh) {
+              if (hh < per) {
+                const float4 a = *reinterpret_cast<const float4*>(qb + (long long)hh * hd);
+                const float4 b = *reinterpret_cast<const float4*>(qb + (long long)hh * hd + 4);
+                float d = into[s][hh];
+                d = fmaf(a.x, kf[0], d); d = fmaf(a.y, kf[1], d); d = fmaf(a.z, kf[2], d); d = fmaf(a.w, kf[3], d);
+                d = fmaf(b.x, kf[4], d); d = fmaf(b.y, kf[5], d); d = fmaf(b.z, kf[6], d); d = fmaf(b.w, kf[7], d);
+                into[s][hh] = d;
+              }
             }
           }
+        };
+        int e = 0;
+        for (; e + 16 <= hd; e += 16) {
+          run(e, dot);
+          run(e + 8, dot2);
         }
+        if (e < hd) run(e, dot);
+#pragma unroll
+        for (int s = 0; s < US; ++s)
+#pragma unroll
+          for (int hh = 0; hh < PER; ++hh) dot[s][hh] += dot2[s][hh];
       } else {
         for (int e = 0; e < hd; ++e) {
-          const float kf = __bfloat162float(krow[e]);
 #pragma unroll
-          for (int hh = 0; hh < PER; ++hh)
-            if (hh < per) dot[hh] = fmaf(qb[(long long)hh * hd + e], kf, dot[hh]);
+          for (int s = 0; s < US; ++s) {
+            if (!u_on[s]) continue;
+            const float kf = __bfloat162float(Ks[((long long)u_c[s] * TK + lane) * KST + e]);
+            const float* qb = qs + ((long long)u_i[s] * nh + (long long)u_c[s] * per) * hd + e;
+#pragma unroll
+            for (int hh = 0; hh < PER; ++hh)
+              if (hh < per) dot[s][hh] = fmaf(qb[(long long)hh * hd], kf, dot[s][hh]);
+          }
         }
       }
+      const int j = kt * TK + lane;
 #pragma unroll
-      for (int hh = 0; hh < PER; ++hh) {
-        if (hh < per) {
-          const int h = c * per + hh;
-          float sc = dot[hh] * scale;
-          if (softcap > 0.f) sc = softcap * tanhf(sc * inv_cap);
-          Ps[((long long)i * nh + h) * TK + lane] = valid ? 1.0f / (1.0f + expf(-(sc + hbs[h]))) : 0.f;
+      for (int s = 0; s < US; ++s) {
+        if (!u_on[s]) continue;
+        const int pos_i = pos0 + u_i[s];
+        const int lo_i = window > 0 ? max(0, pos_i - window + 1) : 0;
+        const bool valid = j >= lo_i && j <= pos_i;
+#pragma unroll
+        for (int hh = 0; hh < PER; ++hh) {
+          if (hh < per) {
+            const int h = u_c[s] * per + hh;
+            float sc = dot[s][hh] * scale;
+            if (softcap > 0.f) sc = softcap * tanhf(sc * inv_cap);
+            Ps[((long long)u_i[s] * nh + h) * TK + lane] = valid ? __fdividef(1.0f, 1.0f + __expf(-(sc + hbs[h]))) : 0.f;
+          }
         }
       }
     }
     __syncthreads();
-    // ---- mix and values, unit by unit
+    // ---- mix: W[i, h, key] for the heads of the warp's units
+    {
+      float wm[US][PER];
 #pragma unroll
-    for (int s = 0; s < US; ++s) {
-      const int n = warp + WARPS * s;
-      if (n >= n_q * nkv) break;
-      const int i = n / nkv, c = n - i * nkv;
-      float wm[PER];
+      for (int s = 0; s < US; ++s)
 #pragma unroll
-      for (int hh = 0; hh < PER; ++hh) wm[hh] = 0.f;
-      const float* pi = Ps + (long long)i * nh * TK + lane;
-      for (int g = 0; g < nh; ++g) {
-        const float pv = pi[g * TK];
+        for (int hh = 0; hh < PER; ++hh) wm[s][hh] = 0.f;
+      if ((nh & 3) == 0) {
+#pragma unroll 2
+        for (int g = 0; g < nh; g += 4) {               // four heads' weights and four values of a row of the mix at a time
+#pragma unroll
+          for (int s = 0; s < US; ++s) {
+            if (!u_on[s]) continue;
+            const float* pi = Ps + ((long long)u_i[s] * nh + g) * TK + lane;
+            const float p0 = pi[0], p1 = pi[TK], p2 = pi[2 * TK], p3 = pi[3 * TK];
+#pragma unroll
+            for (int hh = 0; hh < PER; ++hh) {
+              if (hh < per) {
+                const float4 m4 = *reinterpret_cast<const float4*>(Ms + (u_c[s] * per + hh) * nh + g);
+                float w = wm[s][hh];
+                w = fmaf(m4.x, p0, w); w = fmaf(m4.y, p1, w); w = fmaf(m4.z, p2, w); w = fmaf(m4.w, p3, w);
+                wm[s][hh] = w;
+              }
+            }
+          }
+        }
+      } else {
+        for (int g = 0; g < nh; ++g) {
+#pragma unroll
+          for (int s = 0; s < US; ++s) {
+            if (!u_on[s]) continue;
+            const float pv = Ps[((long long)u_i[s] * nh + g) * TK + lane];
+#pragma unroll
+            for (int hh = 0; hh < PER; ++hh)
+              if (hh < per) wm[s][hh] = fmaf(Ms[(u_c[s] * per + hh) * nh + g], pv, wm[s][hh]);
+          }
+        }
+      }
+#pragma unroll
+      for (int s = 0; s < US; ++s) {
+        if (!u_on[s]) continue;
 #pragma unroll
         for (int hh = 0; hh < PER; ++hh)
-          if (hh < per) wm[hh] = fmaf(Ms[(c * per + hh) * nh + g], pv, wm[hh]);
+          if (hh < per) Ws[((long long)u_i[s] * nh + (long long)u_c[s] * per + hh) * TK + lane] = wm[s][hh];
       }
-      float* wrow = Ws + ((long long)i * nh + (long long)c * per) * TK;
+    }
+    __syncwarp();
+    // ---- values: the warp's own rows of W meet the values, four keys at a time
+#pragma unroll 2
+    for (int jj = 0; jj < TK; jj += 4) {
 #pragma unroll
-      for (int hh = 0; hh < PER; ++hh)
-        if (hh < per) wrow[hh * TK + lane] = wm[hh];
-      __syncwarp();
-      const bf16* vb = Vs + (long long)c * TK * VROW + lane * VPL;
-      for (int jj = 0; jj < TK; jj += 4) {
+      for (int s = 0; s < US; ++s) {
+        if (!u_on[s]) continue;
+        const float* wrow = Ws + ((long long)u_i[s] * nh + (long long)u_c[s] * per) * TK + jj;
+        const bf16* vb = Vs + ((long long)u_c[s] * TK + jj) * VROW + lane * VPL;
         float4 w4[PER];
 #pragma unroll
         for (int hh = 0; hh < PER; ++hh)
-          w4[hh] = hh < per ? *reinterpret_cast<const float4*>(wrow + hh * TK + jj) : make_float4(0.f, 0.f, 0.f, 0.f);
+          w4[hh] = hh < per ? *reinterpret_cast<const float4*>(wrow + hh * TK) : make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
         for (int x = 0; x < 4; ++x) {
           float v[VPL];
-          load_run<VPL>(vb + (long long)(jj + x) * VROW, v);
+          load_run<VPL>(vb + (long long)x * VROW, v);
 #pragma unroll
           for (int hh = 0; hh < PER; ++hh) {
             const float w = x == 0 ? w4[hh].x : x == 1 ? w4[hh].y : x == 2 ? w4[hh].z : w4[hh].w;
@@ -283,15 +358,14 @@ mixed_heads_attention_kernel(const float* q, long long q_stride, const bf16* kv,
           }
         }
       }
-      __syncwarp();
     }
+    __syncwarp();
   }
   // ---- out
 #pragma unroll
   for (int s = 0; s < US; ++s) {
-    const int n = warp + WARPS * s;
-    if (n >= n_q * nkv) break;
-    const int i = n / nkv, c = n - i * nkv;
+    if (!u_on[s]) continue;
+    const int i = u_i[s], c = u_c[s];
 #pragma unroll
     for (int hh = 0; hh < PER; ++hh) {
       if (hh >= per) continue;
@@ -348,10 +422,13 @@ FMX_EXPORT int fmx_mixattn_plan(int n_tokens, int nh, int nkv, int hd, int vd, i
   if (plan_tile(nh, nkv, hd, vd, max_q_len, &us) == 0) return 0;
   if (max_q_len > 1 || n_tokens <= 0) return 1;
   const int tiles = (max_ctx + TK - 1) / TK;
-  const int want = (2 * fmx_num_sms() + n_tokens - 1) / n_tokens;
-  int splits = want < 1 ? 1 : want;
-  if (splits > tiles / 4) splits = tiles / 4;           // at least four tiles of keys per block
-  if (splits > 16) splits = 16;
+  // as many blocks as are resident at once (two per multiprocessor where their shared memory allows), no more: a
+  // second round of a few blocks would double the time
+  const size_t smem = layout_for(1, nh, nkv, hd).total;
+  const int slots = fmx_num_sms() * (2 * smem + 4096 <= 227 * 1024 ? 2 : 1);
+  int splits = slots / n_tokens;
+  if (splits > tiles / 2) splits = tiles / 2;           // at least two tiles of keys per block
+  if (splits > 32) splits = 32;
   return splits < 1 ? 1 : splits;
 }
 

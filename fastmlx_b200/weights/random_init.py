@@ -40,7 +40,7 @@ def random_tensor(seed: int, name: str, shape, kind: str, dtype=torch.bfloat16, 
     elif kind == "alpha":                   # the scalar of a dynamic tanh: between 0.5 and 1.5
         t = torch.sigmoid(t) + 0.5
     elif kind == "head_mix":                # a matrix that mixes heads: near the identity
-        t = torch.eye(shape[0]) + t * 0.1
+        t = torch.eye(shape[0], device=t.device) + t * 0.1
     elif kind == "head_bias":               # a number added to a head's scores in front of a sigmoid: weights well below one
         t = t * 0.5 - 3.0
     elif kind == "norm0":                   # a norm weight stored around zero
