@@ -160,37 +160,44 @@ mixed_heads_attention_kernel(const float* q, long long q_stride, const bf16* kv,
   // rows of a tile are copied by groups of lanes: `lpr` lanes (a power of two) take a row's 16-byte pieces
   const int kc = hd / 8, vc = vd / 8, cpr = kc + vc;
   int lpr_log = 0;
-  while ((1 << lpr_log) < cpr && lpr_log < 5) ++lpr_log;
-  const int lpr = 1 << lpr_log, rpi = 32 >> lpr_log;                 // lanes per row, rows per warp and pass
+  while ((1 << lpr_log) < cpr) ++lpr_log;
+  const int lpr = 1 << lpr_log;                                      // lanes per row
   const int page_log = (page_size & (page_size - 1)) == 0 ? 31 - __clz(page_size) : -1;
 
   for (int kt = kt_first; kt < kt_end; ++kt) {
     __syncthreads();                                    // the tile before is done with K, V and P (and q, M are written)
     // ---- load: rows (c, jj) of keys and of values
     if (kvec) {
-      // 16-byte asynchronous copies, all of a thread's in flight together; a row out of sight is filled with zeros
-      const int sub = lane >> lpr_log, ch0 = lane & (lpr - 1);
-      for (int r = warp * rpi + sub; r < nkv * TK; r += WARPS * rpi) {
-        const int c = r / TK, jj = r - c * TK;
+      // 16-byte asynchronous copies, all of a thread's in flight together; a row out of sight is filled with zeros.
+      // A thread owns (key of the tile, 16-byte piece of a row) pairs: it looks the key's page up once and then walks
+      // the key/value heads, whose rows lie a fixed distance apart in the page and in shared memory
+      for (int idx = threadIdx.x; idx < (TK << lpr_log); idx += blockDim.x) {
+        const int jj = idx >> lpr_log, ch = idx & (lpr - 1);
+        if (ch >= cpr) continue;
         const int j = kt * TK + jj;
-        const bf16* ksrc = nullptr;
-        const bf16* vsrc = nullptr;
+        const bf16* src = kv;
+        unsigned bytes = 0;
+        long long step = 0;
+        const bool is_k = ch < kc;
         if (j >= lo_min && j <= pos_last) {
           const int blk = page_log >= 0 ? j >> page_log : j / page_size;
           const int page = blk < bt_stride ? bt[blk] : -1;
           if (page < 0 || page >= num_pages) {
             fmx_set_status(status, FMX_BAD_PAGE, page, t0);
           } else {
-            const long long at = (long long)c * page_size + (j - blk * page_size);
-            ksrc = kv + (long long)page * page_elems + at * hd;
-            vsrc = kv + (long long)page * page_elems + plane + at * vd;
+            const int at = j - blk * page_size;
+            src = is_k ? kv + (long long)page * page_elems + (long long)at * hd + ch * 8
+                       : kv + (long long)page * page_elems + plane + (long long)at * vd + (ch - kc) * 8;
+            step = (long long)page_size * (is_k ? hd : vd);
+            bytes = 16;
           }
         }
-        for (int ch = ch0; ch < cpr; ch += lpr) {
-          const bf16* src = ksrc == nullptr ? kv : (ch < kc ? ksrc + ch * 8 : vsrc + (ch - kc) * 8);
-          bf16* dst = ch < kc ? Ks + (long long)r * KST + ch * 8 : Vs + (long long)r * VROW + (ch - kc) * 8;
-          const unsigned sa = (unsigned)__cvta_generic_to_shared(dst);
-          asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(sa), "l"(src), "r"(ksrc == nullptr ? 0u : 16u));
+        unsigned sa = (unsigned)__cvta_generic_to_shared(is_k ? Ks + (long long)jj * KST + ch * 8 : Vs + (long long)jj * VROW + (ch - kc) * 8);
+        const unsigned sstep = (unsigned)(TK * (is_k ? KST : VROW) * 2);
+        for (int c = 0; c < nkv; ++c) {
+          asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(sa), "l"(src), "r"(bytes));
+          sa += sstep;
+          src += step;
         }
       }
       asm volatile("cp.async.commit_group;\n" ::);
