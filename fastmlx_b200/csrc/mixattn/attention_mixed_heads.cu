@@ -27,6 +27,9 @@
 #ifndef FMX_VPL
 #define FMX_VPL 2
 #endif
+#ifndef FMX_USP_MAX
+#define FMX_USP_MAX 2
+#endif
 #ifndef FMX_PER
 #define FMX_PER 4
 #endif
@@ -34,7 +37,8 @@
 namespace {
 constexpr int VPL = FMX_VPL, PER = FMX_PER;
 constexpr int WARPS = 8, TK = 32;
-constexpr int USP = (64 / (VPL * PER)) < 1 ? 1 : ((64 / (VPL * PER)) > 4 ? 4 : (64 / (VPL * PER)));
+constexpr int USP_MAX = FMX_USP_MAX;
+constexpr int USP = (64 / (VPL * PER)) < 1 ? 1 : ((64 / (VPL * PER)) > USP_MAX ? USP_MAX : (64 / (VPL * PER)));
 constexpr int VROW = 32 * VPL + 8;                // a value row in shared memory: padded to the lanes' runs, plus 16 bytes
 constexpr size_t SMEM_LIMIT = 220 * 1024;
 
@@ -85,8 +89,8 @@ __host__ __device__ inline Layout layout_for(int TQ, int nh, int nkv, int hd) {
   return L;
 }
 
-template <int US>
-__global__ void __launch_bounds__(WARPS * 32)
+template <int US, int NW>
+__global__ void __launch_bounds__(NW * 32)
 mixed_heads_attention_kernel(const float* q, long long q_stride, const bf16* kv, const int* block_tables, int bt_stride,
                              const int* token_row, const int* positions, const int* row_start, float* part, bf16* out,
                              long long out_stride, int n_tokens, int nh, int nkv, int hd, int vd, int page_size,
@@ -152,7 +156,7 @@ mixed_heads_attention_kernel(const float* q, long long q_stride, const bf16* kv,
   bool u_on[US];
 #pragma unroll
   for (int s = 0; s < US; ++s) {
-    const int n = warp + WARPS * s;
+    const int n = warp + NW * s;
     u_on[s] = n < n_q * nkv;
     u_i[s] = u_on[s] ? n / nkv : 0;
     u_c[s] = u_on[s] ? n - u_i[s] * nkv : 0;
@@ -401,20 +405,31 @@ __global__ void mixed_heads_combine_kernel(const float* part, bf16* out, long lo
   }
 }
 
-// Tokens per tile and units per warp for a step whose longest row brings max_q_len tokens; 0: the sizes do not fit.
-int plan_tile(int nh, int nkv, int hd, int vd, int max_q_len, int* us_out) {
+// Tokens per tile, units per warp and warps per block for a step whose longest row brings max_q_len tokens; 0: the sizes
+// do not fit.  Portions run 8 warps where two blocks fit a multiprocessor's shared memory, else 16 warps in one block.
+int plan_tile(int nh, int nkv, int hd, int vd, int max_q_len, int* us_out, int* nw_out) {
   if (nh <= 0 || nkv <= 0 || nh % nkv || nh / nkv > PER || vd > 32 * VPL || hd <= 0) return 0;
-  const int need = (nkv + WARPS - 1) / WARPS;           // units per warp that one token needs
+  int nw = WARPS;
+  const int need = (nkv + nw - 1) / nw;                 // units per warp that one token needs
   int us = max_q_len > 1 ? USP : 1;
   if (need > us) us = USP;
   if (need > us) return 0;
-  int tq = (WARPS * us) / nkv;
-  if (tq < 1) tq = 1;
-  if (tq > max_q_len) tq = max_q_len > 0 ? max_q_len : 1;
-  while (tq > 1 && layout_for(tq, nh, nkv, hd).total > SMEM_LIMIT) --tq;
+  auto tokens = [&](int warps) {
+    int t = (warps * us) / nkv;
+    if (t < 1) t = 1;
+    if (t > max_q_len) t = max_q_len > 0 ? max_q_len : 1;
+    while (t > 1 && layout_for(t, nh, nkv, hd).total > SMEM_LIMIT) --t;
+    return t;
+  };
+  int tq = tokens(nw);
   if (layout_for(tq, nh, nkv, hd).total > SMEM_LIMIT) return 0;
-  if (us == USP && USP > 1 && (tq * nkv + WARPS - 1) / WARPS <= 1) us = 1;
+  if (max_q_len > 1 && 2 * layout_for(tq, nh, nkv, hd).total + 4096 > 227 * 1024) {
+    const int tq16 = tokens(2 * WARPS);                 // one block per multiprocessor either way: twice the warps
+    if (tq16 * nkv > WARPS * us) { nw = 2 * WARPS; tq = tq16; }
+  }
+  if (us == USP && USP > 1 && (tq * nkv + nw - 1) / nw <= 1) us = 1;
   *us_out = us;
+  *nw_out = nw;
   return tq;
 }
 }  // namespace
@@ -425,8 +440,8 @@ FMX_EXPORT int fmx_mixattn_per() { return PER; }
 // How many blocks a token's keys should be shared out over (1 for portions), or 0 where the kernel does not take
 // the sizes (the caller then uses the kernel with one warp per token and head).
 FMX_EXPORT int fmx_mixattn_plan(int n_tokens, int nh, int nkv, int hd, int vd, int max_q_len, int max_ctx) {
-  int us = 1;
-  if (plan_tile(nh, nkv, hd, vd, max_q_len, &us) == 0) return 0;
+  int us = 1, nw = WARPS;
+  if (plan_tile(nh, nkv, hd, vd, max_q_len, &us, &nw) == 0) return 0;
   if (max_q_len > 1 || n_tokens <= 0) return 1;
   const int tiles = (max_ctx + TK - 1) / TK;
   // as many blocks as are resident at once (two per multiprocessor where their shared memory allows), no more: a
@@ -451,8 +466,8 @@ FMX_EXPORT int fmx_mixattn(const float* q, long long q_stride, const void* kv, c
   if (n_tokens < 0 || page_size <= 0 || window < 0 || splits < 1 || (splits > 1 && part == nullptr) || mix == nullptr)
     return fmx_fail("fmx_mixattn: bad sizes T=%d page=%d window=%d splits=%d", n_tokens, page_size, window, splits);
   if (out_stride < (long long)nh * vd) return fmx_fail("fmx_mixattn: output rows too narrow");
-  int us = 1;
-  const int tq = plan_tile(nh, nkv, hd, vd, max_q_len, &us);
+  int us = 1, nw = WARPS;
+  const int tq = plan_tile(nh, nkv, hd, vd, max_q_len, &us, &nw);
   if (tq == 0) return fmx_fail("fmx_mixattn: sizes nh=%d nkv=%d hd=%d vd=%d do not fit this library (%d values per lane, %d heads per key head)",
                                nh, nkv, hd, vd, VPL, PER);
   if (((uintptr_t)q & 15) || (q_stride & 3) || ((nh * hd) & 3)) return fmx_fail("fmx_mixattn: queries must lie on 16 bytes");
@@ -464,14 +479,16 @@ FMX_EXPORT int fmx_mixattn(const float* q, long long q_stride, const void* kv, c
       if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_LIMIT) != cudaSuccess) return 1;
       raised = (void*)kernel;
     }
-    fmx_launch(kernel, grid, dim3(WARPS * 32), L.total, stream, q, q_stride, (const bf16*)kv, block_tables, bt_stride, token_row,
+    fmx_launch(kernel, grid, dim3(nw * 32), L.total, stream, q, q_stride, (const bf16*)kv, block_tables, bt_stride, token_row,
                positions, row_start, part, (bf16*)out, out_stride, n_tokens, nh, nkv, hd, vd, page_size, num_pages, scale,
                softcap, window, R, head_bias, mix, tq, splits, status);
     return 0;
   };
   int rc;
-  if (us == 1) rc = launch(mixed_heads_attention_kernel<1>);
-  else rc = launch(mixed_heads_attention_kernel<USP>);
+  if (us == 1 && nw == WARPS) rc = launch(mixed_heads_attention_kernel<1, WARPS>);
+  else if (us == 1) rc = launch(mixed_heads_attention_kernel<1, 2 * WARPS>);
+  else if (nw == WARPS) rc = launch(mixed_heads_attention_kernel<USP, WARPS>);
+  else rc = launch(mixed_heads_attention_kernel<USP, 2 * WARPS>);
   if (rc) return fmx_fail("fmx_mixattn: the kernel's shared memory could not be raised");
   FMX_LAUNCH_CHECK();
   if (splits > 1) {
