@@ -240,16 +240,59 @@ FMX_EXPORT int fmx_moe_expert_act(const void* gu, long long gu_stride, const flo
   return 0;
 }
 
+namespace {
+// moe_plain_act for bfloat16 rows in 16-byte pieces (eight columns of one expert: ff and the experts' columns are multiples of 8).
+__global__ void moe_plain_act_vec_kernel(const bf16* u, long long u_stride, const float* weights, const float* shared_gate,
+                                         long long sg_stride, bf16* out, long long out_stride, long long rows, int E, int ff,
+                                         int F, int act) {
+  pdl_wait();
+  pdl_trigger();
+  const int f8 = F / 8;
+  const long long n = rows * f8;
+  for (long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x; idx < n; idx += (long long)gridDim.x * blockDim.x) {
+    const long long r = idx / f8;
+    const int c = (int)(idx - r * f8) * 8;
+    const int e = c / ff;
+    float w;
+    if (e < E) w = weights[r * E + e];
+    else w = shared_gate != nullptr ? 1.0f / (1.0f + expf(-shared_gate[r * sg_stride])) : 1.0f;
+    uint4 o = make_uint4(0u, 0u, 0u, 0u);
+    if (w != 0.f) {
+      const uint4 u4 = *reinterpret_cast<const uint4*>(u + r * u_stride + c);
+      const __nv_bfloat162* up = reinterpret_cast<const __nv_bfloat162*>(&u4);
+      __nv_bfloat162* op = reinterpret_cast<__nv_bfloat162*>(&o);
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const float2 x = __bfloat1622float2(up[i]);
+        float a0, a1;
+        if (act == 0) { const float p0 = fmaxf(x.x, 0.f), p1 = fmaxf(x.y, 0.f); a0 = p0 * p0; a1 = p1 * p1; }
+        else if (act == 1) {
+          a0 = 0.5f * x.x * (1.0f + tanhf(0.7978845608028654f * (x.x + 0.044715f * x.x * x.x * x.x)));
+          a1 = 0.5f * x.y * (1.0f + tanhf(0.7978845608028654f * (x.y + 0.044715f * x.y * x.y * x.y)));
+        } else { a0 = x.x / (1.0f + expf(-x.x)); a1 = x.y / (1.0f + expf(-x.y)); }
+        op[i] = __floats2bfloat162_rn(w * a0, w * a1);
+      }
+    }
+    *reinterpret_cast<uint4*>(out + r * out_stride + c) = o;
+  }
+}
+}  // namespace
+
 FMX_EXPORT int fmx_moe_plain_act(const void* u, long long u_stride, const float* weights, const float* shared_gate,
                                  long long sg_stride, void* out, long long out_stride, int rows, int E, int ff, int F, int act,
                                  int dtype, cudaStream_t stream) {
   if (rows == 0 || F == 0) return 0;
   if (rows < 0 || E < 0 || ff <= 0 || F < E * ff || u_stride < F || out_stride < F || act < 0 || act > 2)
     return fmx_fail("fmx_moe_plain_act: bad sizes rows=%d E=%d ff=%d F=%d act=%d", rows, E, ff, F, act);
-  const long long n = (long long)rows * F, cap = (long long)fmx_num_sms() * 16;
+  const bool vec = dtype == FMX_BF16 && F % 8 == 0 && ff % 8 == 0 && (E * ff) % 8 == 0 && u_stride % 8 == 0 && out_stride % 8 == 0 &&
+                   ((uintptr_t)u & 15) == 0 && ((uintptr_t)out & 15) == 0;
+  const long long n = (long long)rows * (vec ? F / 8 : F), cap = (long long)fmx_num_sms() * 16;
   const int block = 256;
   const int grid = (int)((n + block - 1) / block < cap ? (n + block - 1) / block : cap);
-  if (dtype == FMX_F32)
+  if (vec)
+    fmx_launch(moe_plain_act_vec_kernel, dim3(grid), dim3(block), 0, stream, (const bf16*)u, u_stride, weights, shared_gate, sg_stride,
+               (bf16*)out, out_stride, (long long)rows, E, ff, F, act);
+  else if (dtype == FMX_F32)
     fmx_launch(moe_plain_act_kernel<float>, dim3(grid), dim3(block), 0, stream, (const float*)u, u_stride, weights, shared_gate,
                sg_stride, (float*)out, out_stride, (long long)rows, E, ff, F, act);
   else if (dtype == FMX_BF16)

@@ -345,12 +345,13 @@ def test_router_choice_by_corrected_scores_and_plain_experts():
     corrected = plain_ops.moe_route(z, 3, want_chosen=True, experts=E, correction=corr)[1].long().sort(1).values
     assert not torch.equal(plain_top, corrected), "the correction changes no choice: the test shows nothing"
     for dtype in (torch.float32, torch.bfloat16):
-        u = torch.randn(T, E * 6 + 9, generator=g).to(dtype)
-        for act in ("relu2", "gelu_tanh", "silu"):
-            for gate in (z[:, E:], None):
-                got = k.moe_plain_act(u.cuda(), ww.cuda(), E, 6, act, shared_gate=_dev(gate)).cpu().double()
-                want = plain_ops.moe_plain_act(u.double(), ww, E, 6, act, shared_gate=gate)
-                assert (got - want).abs().max() <= (1e-6 if dtype == torch.float32 else 1e-2) * want.abs().max()
+        for ff, shared in ((6, 9), (16, 24)):                                       # the second in 16-byte pieces
+            u = torch.randn(T, E * ff + shared, generator=g).to(dtype)
+            for act in ("relu2", "gelu_tanh", "silu"):
+                for gate in (z[:, E:], None):
+                    got = k.moe_plain_act(u.cuda(), ww.cuda(), E, ff, act, shared_gate=_dev(gate)).cpu().double()
+                    want = plain_ops.moe_plain_act(u.double(), ww, E, ff, act, shared_gate=gate)
+                    assert (got - want).abs().max() <= (1e-6 if dtype == torch.float32 else 1e-2) * want.abs().max()
 
 
 def test_scaled_embedding_starts_the_stream_in_32_bit():
