@@ -449,13 +449,13 @@ def kafepel_like(shape: dict, layers: int) -> dict:
     of half of it."""
     d, nh, nkv, hd = shape["hidden_size"], shape["num_attention_heads"], shape["num_key_value_heads"], shape["head_dim"]
     ff = shape["intermediate_size"]
-    rot = {"dims": hd, "base": 1000000.0, "scaling": {"factor": 8.0, "low": 1.0, "high": 4.0, "original": 8192}}
-    mixer = {"left": {"heads": nh, "kv_heads": nkv, "dim": hd, "vdim": hd, "scale": hd ** -0.5, "softcap": 50.0, "rot": rot},
+    rot = {"dims": hd, "base": 500000.0, "scaling": {"factor": 8.0, "low": 1.0, "high": 4.0, "original": 8192}}
+    mixer = {"left": {"heads": nh, "kv_heads": nkv, "dim": hd, "vdim": hd, "scale": hd ** -0.5, "softcap": 30.0, "rot": rot},
              "right": {"heads": nh, "dim": hd, "vdim": hd, "decay": [1.0 - 2.0 ** -(5 + 3 * i / max(1, nh - 1)) for i in range(nh)],
-                       "rot": {"dims": hd, "base": 1000000.0}}}
+                       "rot": {"dims": hd, "base": 500000.0}}}
     dense = {"kind": "dense", "ff": ff}
-    moe = {"kind": "moe", "router": {"experts": 8, "top": 2, "scale": 2.5}, "expert": {"ff": ff // 4}, "shared": {"ff": ff // 2}}
-    return {"architecture": "Kafepel", "vocab": shape["vocab_size"], "width": d, "norm": {"eps": 1e-6}, "embedding": {"scale": 0.5},
+    moe = {"kind": "moe", "router": {"experts": 8, "top": 2, "scale": 2.0}, "expert": {"ff": ff // 4}, "shared": {"ff": ff // 2}}
+    return {"architecture": "Kafepel", "vocab": shape["vocab_size"], "width": d, "norm": {"eps": 1e-6}, "embedding": {"scale": 2.0},
             "layers": [{"type": "parallel", "mixer": mixer, "mlp": moe if i % 2 else dense} for i in range(layers)]}
 
 

@@ -65,9 +65,8 @@ class RotaryConfig:
             w = where + ".rot.scaling"
             scaling = RopeScaling("llama3", _float(sc, "factor", w), _float(sc, "low", w), _float(sc, "high", w),
                                   _int(sc, "original", w))
-            if scaling.factor <= 0 or scaling.high_freq_factor == scaling.low_freq_factor or scaling.low_freq_factor <= 0 \
-                    or scaling.high_freq_factor <= 0:
-                raise ConfigError(f"kafepel: {w}: factor, low and high must be positive and low must differ from high")
+            if scaling.factor <= 0 or scaling.low_freq_factor <= 0 or scaling.high_freq_factor <= 0:
+                raise ConfigError(f"kafepel: {w}: factor, low and high must be positive")
         return RotaryConfig(dims, base, scaling)
 
 
@@ -90,8 +89,8 @@ class SigmoidAttentionConfig:
             RotaryConfig.from_dict(d, where, dim))
         if c.heads % c.kv_heads:
             raise ConfigError(f"kafepel: {where}: {c.heads} heads are no multiple of {c.kv_heads} kv_heads")
-        if c.softcap < 0 or c.dim > 512 or c.vdim > 512:
-            raise ConfigError(f"kafepel: {where}: softcap >= 0 and head sizes up to 512")
+        if c.softcap < 0 or c.dim > 256 or c.vdim > 512:
+            raise ConfigError(f"kafepel: {where}: softcap >= 0, keys up to 256 and values up to 512 wide")
         return c
 
 

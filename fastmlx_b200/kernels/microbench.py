@@ -191,10 +191,10 @@ def _attn_mixed(a) -> int:
     every = sum(p + 1 for p in range(c, c + q)) * B                          # (query, key) pairs in sight
     fma = every * (nh * hd + nh * nh + nh * hd)                              # scores, the mix, the values: 32-bit multiply-adds
     kvb = B * (c + q) * nkv * hd * 2 * 2
-    cases = [("tiled", lambda: k.sigmoid_attention(qq, kv, ctx, grp, nh, nkv, hd, hd, hd ** -0.5, 50.0, 0, ps, bias, mix, tiled=True))]
+    cases = [("tiled", lambda: k.sigmoid_attention(qq, kv, ctx, grp, nh, nkv, hd, hd, hd ** -0.5, 30.0, 0, ps, bias, mix, tiled=True))]
     if a.simple:
         cases.append(("one warp per token, head and value head",
-                      lambda: k.sigmoid_attention(qq, kv, ctx, grp, nh, nkv, hd, hd, hd ** -0.5, 50.0, 0, ps, bias, mix, tiled=False)))
+                      lambda: k.sigmoid_attention(qq, kv, ctx, grp, nh, nkv, hd, hd, hd ** -0.5, 30.0, 0, ps, bias, mix, tiled=False)))
     for name, fn in cases:
         us = _time_events(fn, a.replays, flush)
         print(f"attn_mixed {name} B={B} qlen={q} ctx={c} nh={nh} nkv={nkv} hd={hd}: {us:.1f} us, {fma / us / 1e6:.2f} TFMA/s of "

@@ -336,8 +336,8 @@ def test_router_choice_by_corrected_scores_and_plain_experts():
     z[3, :E] = 0.0                                                                  # a tie of all: the lower indices win
     corr = torch.randn(E, generator=g) * 0.2
     for top in (1, 3, E):
-        w, chosen = k.moe_route(z.cuda(), top, want_chosen=True, experts=E, correction=corr.cuda(), scale=2.5)
-        ww, wc = plain_ops.moe_route(z, top, want_chosen=True, experts=E, correction=corr, scale=2.5)
+        w, chosen = k.moe_route(z.cuda(), top, want_chosen=True, experts=E, correction=corr.cuda(), scale=1.5)
+        ww, wc = plain_ops.moe_route(z, top, want_chosen=True, experts=E, correction=corr, scale=1.5)
         assert torch.equal(chosen.cpu(), wc) and (w.cpu() - ww).abs().max() < 1e-6
         assert (w.cpu() > 0).sum(1).eq(top).all()
     s = torch.softmax(z[:, :E], -1)

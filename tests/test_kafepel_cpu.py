@@ -33,7 +33,7 @@ def test_registry_finds_the_design_and_builds_its_layers():
     assert a.pos.rotary_dim == 8 and a.pos.scaling.factor == 8.0 and a.pos.scaling.original_max_position_embeddings == 64
     assert (r.H, r.D, r.P, r.decay_values, r.rot_dims, r.rot_base) == (3, 12, 20, (0.9, 0.97, 0.75), 12, 500.0)
     e = model.layers[1].ffn
-    assert (e.E, e.top, e.ff, e.scale, e.shared_ff, e.activation) == (6, 2, 24, 2.5, 40, "relu2")
+    assert (e.E, e.top, e.ff, e.scale, e.shared_ff, e.activation) == (6, 2, 24, 1.75, 40, "relu2")
     assert model.layers[2].ffn.shared_ff == 0 and model.layers[2].ffn.gate_name is None
     assert model.layers[2].mixer.left.softcap == 30.0 and model.layers[1].mixer.left.softcap == 0.0
     # no embedding block: no multiplier, and the embedding is the plain gather
@@ -79,7 +79,7 @@ def test_tensor_names_and_shapes():
     lambda c: c["layers"][0]["mixer"]["left"].update(kv_heads=3),
     lambda c: c["layers"][0]["mixer"]["left"]["rot"].update(dims=7),
     lambda c: c["layers"][0]["mixer"]["left"]["rot"].update(dims=26),
-    lambda c: c["layers"][0]["mixer"]["left"]["rot"]["scaling"].update(high=1.0),
+    lambda c: c["layers"][0]["mixer"]["left"]["rot"]["scaling"].update(factor=0),
     lambda c: c["layers"][0]["mixer"]["right"].update(decay=[0.5, 0.5]),
     lambda c: c["layers"][0]["mixer"]["right"].update(decay=[0.5, 0.5, 1.5]),
     lambda c: c["layers"][0]["mixer"].pop("right"),
@@ -174,7 +174,7 @@ def test_plain_retention_equals_its_sum_over_earlier_tokens():
 
 
 def test_plain_router_chooses_by_corrected_scores_and_weighs_by_scores():
-    mlp = tk.moe(4, 2, 2.5, 3, shared=2)
+    mlp = tk.moe(4, 2, 1.5, 3, shared=2)
     width = 5
     W, g = _weights({f"e{e}.{n}": s for e in range(4) for n, s in (("up", (3, width)), ("down", (width, 3)))}, 3)
     W.update(_weights({"router": (4, width), "shared.up": (2, width), "shared.down": (width, 2), "shared.sg": (1, width)}, 4)[0])
@@ -185,7 +185,7 @@ def test_plain_router_chooses_by_corrected_scores_and_weighs_by_scores():
     W["correction"] = torch.zeros(4, dtype=torch.float64)
     W["correction"][order[3]] = 10.0
     y = pk.routed_feed_forward(h, W, mlp)
-    want = sum(2.5 * s[e] * pk.expert(h, pk.sub(W, f"e{e}.")) for e in (order[3], order[0]))
+    want = sum(1.5 * s[e] * pk.expert(h, pk.sub(W, f"e{e}.")) for e in (order[3], order[0]))
     want = want + torch.sigmoid(h @ W["shared.sg"].T) * pk.expert(h, pk.sub(W, "shared."))
     assert torch.allclose(y, want, atol=1e-12)
     assert torch.equal(pk.expert(-torch.ones(1, 1, dtype=torch.float64), {"up": torch.ones(3, 1, dtype=torch.float64),

@@ -50,7 +50,7 @@ K1 = {
     "layers": [
         layer(left(4, 2, 24, 16, 0.3, softcap=7.5, rot=rot(8, 10000.0, (8.0, 1.0, 4.0, 64))),
               right(12, 20, (0.9, 0.97, 0.75), rot=rot(12, 500.0)), dense(160)),
-        layer(left(3, 3, 16, 16, 0.25, rot=rot(16, 50.0)), right(8, 8, (0.5, 1.0, 0.0, 0.99)), moe(6, 2, 2.5, 24, shared=40)),
+        layer(left(3, 3, 16, 16, 0.25, rot=rot(16, 50.0)), right(8, 8, (0.5, 1.0, 0.0, 0.99)), moe(6, 2, 1.75, 24, shared=40)),
         layer(left(6, 1, 8, 24, 0.35, softcap=30.0), right(20, 12, (0.95,), rot=rot(4, 100.0)), moe(5, 1, 0.7, 16)),
         layer(left(2, 1, 32, 32, 0.17, softcap=3.0, rot=rot(32, 500.0, (2.0, 1.0, 2.0, 32))), right(16, 16, (0.8, 0.9), rot=rot(16, 500.0))),
     ],
@@ -66,9 +66,9 @@ K2 = {
 K3 = {
     "architecture": "Kafepel", "vocab": 130, "width": 128, "norm": {"eps": 1e-4}, "embedding": {"scale": 0.25},
     "layers": [
-        layer(left(8, 2, 64, 64, 0.125, softcap=12.0, rot=rot(64, 1000000.0, (4.0, 1.0, 4.0, 128))),
-              right(64, 64, (0.97, 0.98, 0.99, 0.995), rot=rot(64, 1000000.0)), dense(256)),
-        layer(left(4, 4, 64, 64, 0.11, softcap=50.0, rot=rot(16, 30000.0)), right(32, 64, (0.9, 0.99), rot=rot(32, 30000.0)),
+        layer(left(8, 2, 64, 64, 0.125, softcap=12.0, rot=rot(64, 250000.0, (3.0, 1.0, 2.0, 128))),
+              right(64, 64, (0.97, 0.98, 0.99, 0.995), rot=rot(64, 250000.0)), dense(256)),
+        layer(left(4, 4, 64, 64, 0.11, softcap=20.0, rot=rot(16, 30000.0)), right(32, 64, (0.9, 0.99), rot=rot(32, 30000.0)),
               moe(8, 2, 1.5, 64, shared=128)),
         layer(left(2, 1, 128, 64, 0.09, rot=rot(128, 777.0)), right(128, 32, (0.999, 0.5, 0.9), rot=rot(64, 777.0)), moe(4, 3, 2.0, 128)),
     ],
