@@ -31,7 +31,9 @@ delta rule layers to one layer of capped sliding-window attention, a dense feed-
 the Llama layers: a 2,048-token prompt whole and in portions of 512, and steady decoding at batch 8 and 64.
 `--design-set llama,medirax,gekavik` chooses the designs; a Gekavik model of those sizes has windowed attention that
 keeps the first tokens, latent attention in every fourth layer, and a mixture of 32 experts (4 per token and a shared
-one) whose active parameters equal the Llama layer's.
+one) whose active parameters equal the Llama layer's; `sorupel` and `kafepel` name the other two designs (a Kafepel model of
+those sizes: sigmoid attention with mixed heads beside a retention in every layer, gated feed-forwards alternating with a
+mixture of 8 squared-relu experts and a gated shared one).
 
 Every timed step reads well over 126 MB (weights alone are 2.5 GB), so no input stays in L2
 between iterations.  tamnd/fastmlx publishes no number to compare with, and cannot run here
@@ -551,7 +553,7 @@ def main() -> int:
                     "layers of equal size are measured side by side; prints that comparison alone")
     ap.add_argument("--design-layers", type=int, default=8, help="layers of each model of the --designs comparison")
     ap.add_argument("--design-set", default="llama,medirax", help="which designs the --designs comparison measures "
-                    "(comma-separated, of llama, medirax, gekavik, sorupel)")
+                    "(comma-separated, of llama, medirax, gekavik, sorupel, kafepel)")
     ap.add_argument("--only-steps", type=int, default=0,
                     help="for a profiler's launch list: fill the batch, run this many decode steps and stop (no timing, no JSON line); "
                     "with --designs: a 2,048-token prompt step and the decode steps of the first design named, at the first size named")
