@@ -14,13 +14,15 @@
 //   values    the same warp: lane = a run of FMX_VPL value dimensions; acc[h] += W[i, h, key] v_c(key), key by key,
 //             one fetch of a value row for all heads of the unit.  The accumulators stay in registers over all tiles.
 //
-// Queries are 32-bit, keys and values are exact in 32-bit, and every sum (over a head's dimensions, over heads, over
-// keys) is a chain of 32-bit multiply-adds in index order: no tensor cores, because a weight that is a 32-bit sum of
+// Queries are 32-bit, keys and values are exact in 32-bit, and every sum is made of 32-bit multiply-adds in an order that
+// the indices alone fix (over heads and over keys one chain in index order; a dot product two chains, over the even and
+// the odd runs of eight dimensions): no tensor cores, because a weight that is a 32-bit sum of
 // 32-bit sigmoids has no two-term bfloat16 form that the mix would keep.  Nothing is normalised over the keys, so a
 // token's keys may be shared out over `splits` blocks whose partial outputs a second kernel adds up in split order.
 //
 // One library per (FMX_VPL, FMX_PER): FMX_VPL value dimensions per lane (values up to 32 * FMX_VPL wide), FMX_PER query
-// heads per key/value head at most.  US units per warp: 1 (single tokens) or FMX_USP (portions).
+// heads per key/value head at most.  US units per warp: 1 (single tokens) or USP (portions: at most FMX_USP_MAX, so that two
+// blocks of eight warps fit a multiprocessor's registers; sixteen warps where shared memory leaves room for one block only).
 #include <math.h>
 #include "common.cuh"
 
